@@ -21,7 +21,10 @@ Reference for the bookkeeping this replaces: src/wllm/engine/kv_cache.py:63-303
 Pool layout on the device, per group:
     [layer_in_group][k|v][page][kv_head][slot_in_page][head_dim]
 A group whose value heads have a size of their own (`v_head_dim`) holds two pools of that layout
-without the k|v axis, one for keys and one for values.
+without the k|v axis, one for keys and one for values; a group whose values are the first elements of its
+keys' rows (`values_in_keys`) holds the one pool of keys.  A window group may be one of blocks (`blocks`): a
+token reads the earlier keys of its own block of `window` positions, so the pages in front of the block
+that the next token lies in go back.
 """
 from __future__ import annotations
 
@@ -41,6 +44,16 @@ class CacheGroupSpec:
     window: int | None = None   # None: every key is kept; n: a token reads the n latest keys (itself included)
     v_head_dim: int | None = None   # size of a value head when it differs from head_dim
     keep_first: int = 0             # with a window: the first keys of a sequence that stay readable behind it
+    blocks: bool = False            # `window` is a block size: a token reads the earlier keys of its own block of positions
+    values_in_keys: bool = False    # the values are the first v_head_dim elements of the keys' rows: one pool, no k|v axis
+
+    def first_needed(self, num_tokens: int) -> int:
+        """The oldest key that the token at position `num_tokens` (the next one) reads; every key for a group without a mask."""
+        if self.window is None:
+            return 0
+        if self.blocks:
+            return num_tokens - num_tokens % self.window
+        return max(0, num_tokens - self.window + 1)
 
 
 @dataclass(frozen=True)
@@ -78,7 +91,9 @@ class CacheGroup:
             def pool(*shape):
                 return torch.full(shape, float("nan"), dtype=dtype, device=device) if poison else \
                     torch.zeros(shape, dtype=dtype, device=device)
-            if self.v_head_dim == spec.head_dim:
+            if spec.values_in_keys:
+                self.key_pages = self.value_pages = pool(spec.layers, num_pages, spec.kv_heads, page_size, spec.head_dim)
+            elif self.v_head_dim == spec.head_dim:
                 self.pages = pool(spec.layers, 2, num_pages, spec.kv_heads, page_size, spec.head_dim)
             else:
                 self.key_pages = pool(spec.layers, num_pages, spec.kv_heads, page_size, spec.head_dim)
@@ -88,7 +103,7 @@ class CacheGroup:
         """Pages go back to the pool; with `poison` their contents become NaN first (in stream order, so a step
         still running has read them before)."""
         if self.poison and pages:
-            for pool, axis in ((self.pages, 2), (self.key_pages, 1), (self.value_pages, 1)):
+            for pool, axis in ((self.pages, 2), (self.key_pages, 1), (None if self.spec.values_in_keys else self.value_pages, 1)):
                 if pool is not None:
                     pool.index_fill_(axis, torch.tensor(pages, dtype=torch.long, device=pool.device), float("nan"))
         for page in pages:
@@ -101,7 +116,8 @@ class CacheGroup:
         return self.pages[layer, 1] if self.pages is not None else self.value_pages[layer]
 
     def bytes_per_token(self) -> int:
-        return self.spec.layers * self.spec.kv_heads * (self.spec.head_dim + self.v_head_dim) * self._item
+        per_head = self.spec.head_dim if self.spec.values_in_keys else self.spec.head_dim + self.v_head_dim
+        return self.spec.layers * self.spec.kv_heads * per_head * self._item
 
 
 class StateSlots:
@@ -223,7 +239,7 @@ class CacheManager:
             w = g.spec.window
             if w is None:
                 continue
-            first_needed = rc.num_tokens - w + 1          # oldest key the next token reads
+            first_needed = g.spec.first_needed(rc.num_tokens)      # oldest key the next token reads
             upto = min(max(0, first_needed // self.page_size), len(rc.tables[gi]))
             kept = -(-g.spec.keep_first // self.page_size)       # pages that hold a sequence's kept first keys stay
             passed = list(range(max(rc.released_upto[gi], kept), upto))

@@ -79,15 +79,75 @@ WLLM_API int wllm_gated_act(const void* in, void* out, int dtype, int act, int n
     return wllm_gated_act_params(in, out, dtype, act, n, I, 0.f, 0.f, stream);
 }
 
-__global__ void tanh_cap_kernel(float* __restrict__ x, size_t total, float cap) {
+// x <- cap * tanh((x * scale) / cap); cap = 0: x <- x * scale
+__global__ void tanh_cap_kernel(float* __restrict__ x, size_t total, float cap, float scale) {
     pdl_begin();
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x)
-        x[idx] = cap * tanhf(x[idx] / cap);
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const float v = scale == 1.0f ? x[idx] : x[idx] * scale;
+        x[idx] = cap > 0.f ? cap * tanhf(v / cap) : v;
+    }
+}
+
+WLLM_API int wllm_scale_tanh_cap(float* x, long long total, float cap, float scale, cudaStream_t stream) {
+    if (total <= 0) return WLLM_OK;
+    if (!(cap >= 0.f)) return WLLM_BAD_SIZE;
+    const long long want = (total + 255) / 256;
+    return wllm_launch(tanh_cap_kernel, (int)(want < 148 * 16 ? want : 148 * 16), 256, 0, stream, x, (size_t)total, cap, scale);
 }
 
 WLLM_API int wllm_tanh_cap(float* x, long long total, float cap, cudaStream_t stream) {
-    if (total <= 0) return WLLM_OK;
     if (!(cap > 0.f)) return WLLM_BAD_SIZE;
+    return wllm_scale_tanh_cap(x, total, cap, 1.0f, stream);
+}
+
+// A feed-forward unit without a gate: out = act(in), evaluated in 32-bit and rounded once.  act 0: relu(x)^2.
+template <typename T>
+__global__ void unit_act_kernel(const T* __restrict__ in, T* __restrict__ out, size_t total) {
+    pdl_begin();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const float v = fmaxf(to_f32(in[idx]), 0.f);
+        out[idx] = from_f32<T>(v * v);
+    }
+}
+
+WLLM_API int wllm_unit_act(const void* in, void* out, int dtype, int act, long long total, cudaStream_t stream) {
+    if (total <= 0) return WLLM_OK;
+    if (act != 0) return WLLM_BAD_SIZE;
     const long long want = (total + 255) / 256;
-    return wllm_launch(tanh_cap_kernel, (int)(want < 148 * 16 ? want : 148 * 16), 256, 0, stream, x, (size_t)total, cap);
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    if (dtype == WLLM_BF16) return wllm_launch(unit_act_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)in, (bf16*)out, (size_t)total);
+    if (dtype == WLLM_F32) return wllm_launch(unit_act_kernel<float>, blocks, 256, 0, stream, (const float*)in, (float*)out, (size_t)total);
+    return WLLM_BAD_DTYPE;
+}
+
+// The heads' outputs times a sigmoid gate: x[n, c] *= sigmoid(g[n, c]), c < width.  The gate's row comes as `parts` partial
+// sums (slabs `part_stride` elements apart, added in order) or as one tensor; the sigmoid and the product are 32-bit, rounded once.
+template <typename TX, typename TG>
+__global__ void sigmoid_gate_kernel(TX* __restrict__ x, int x_stride, const TG* __restrict__ g, int g_stride, int parts,
+                                    size_t part_stride, int n, int width) {
+    pdl_begin();
+    const size_t total = (size_t)n * width;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / width, c = idx % width;
+        const TG* src = g + t * g_stride + c;
+        float z = to_f32(src[0]);
+        for (int s = 1; s < parts; ++s) z += to_f32(src[(size_t)s * part_stride]);
+        TX* dst = x + t * x_stride + c;
+        *dst = from_f32<TX>(to_f32(*dst) * (1.0f / (1.0f + expf(-z))));
+    }
+}
+
+WLLM_API int wllm_sigmoid_gate(void* x, int x_dtype, int x_stride, const void* g, int g_dtype, int g_stride, int parts,
+                               long long part_stride, int n, int width, cudaStream_t stream) {
+    if (n <= 0) return WLLM_OK;
+    if (width <= 0 || parts < 1) return WLLM_BAD_SIZE;
+    const long long want = ((long long)n * width + 255) / 256;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+#define GO(TX, TG) wllm_launch(sigmoid_gate_kernel<TX, TG>, blocks, 256, 0, stream, (TX*)x, x_stride, (const TG*)g, g_stride, parts, \
+                               (size_t)part_stride, n, width)
+    if (x_dtype == WLLM_BF16 && g_dtype == WLLM_BF16) return GO(bf16, bf16);
+    if (x_dtype == WLLM_BF16 && g_dtype == WLLM_F32) return GO(bf16, float);
+    if (x_dtype == WLLM_F32 && g_dtype == WLLM_F32) return GO(float, float);
+#undef GO
+    return WLLM_BAD_DTYPE;
 }

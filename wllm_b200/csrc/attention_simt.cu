@@ -1,7 +1,8 @@
 // Attention over the paged cache, one warp per (token, query head), every size.
 //
 // A token at position p of request r attends to the keys first..p of r, where
-// first = 0, or p - window + 1 when the layer has a window; the keys are found
+// first = 0, or p - window + 1 when the layer has a window, or the start of p's block of -window positions when `window`
+// is negative (a mask of blocks: see first_visible_key); the keys are found
 // through the request's row of the block table.  The keys and values of this
 // step's own tokens are already in the pages when the kernel runs, so a portion
 // of a prompt, a whole prompt and a single decoded token are the same case.
@@ -37,6 +38,9 @@
 // the chunks of its kept keys (from chunk 0 on) and the chunks of its window, each once, in ascending order; tiles
 // of 32 keys without a visible key are passed by (their pages may have been given back).
 //
+// `v_ld`: elements between two value rows of the pool; with v_ld = hd and v_pages = k_pages the values are the first vd
+// elements of the keys' rows (a cache that holds one row per token for both).
+//
 // Used for the 32-bit path at every size, and for bfloat16 at the sizes that the
 // tensor-core kernels refuse.
 #include "common.cuh"
@@ -71,7 +75,7 @@ template <> struct Vec<bf16> {
 struct RowKeys { int first, kept, first_chunk, last_chunk, head_chunks; };
 __device__ __forceinline__ RowKeys row_keys(int pos, int window, int keep) {
     RowKeys r;
-    r.first = window > 0 ? max(0, pos - window + 1) : 0;
+    r.first = first_visible_key(pos, window);
     r.kept = 0;
     if (keep > 0) {
         if (r.first <= keep) r.first = 0; else r.kept = keep;
@@ -88,7 +92,7 @@ __device__ __forceinline__ int row_chunk_count(const RowKeys& r) { return r.head
 template <typename T, int NE>
 __device__ __forceinline__ void chunk_partial(const float* __restrict__ qs, const T* __restrict__ k_pages,
                                               const T* __restrict__ v_pages, const int* __restrict__ table, int nkv,
-                                              int kvh, int hd, int vd, int page_size, int first, int kept, int pos, int chunk, float scale,
+                                              int kvh, int hd, int vd, int v_ld, int page_size, int first, int kept, int pos, int chunk, float scale,
                                               float cap, int lane, float& m, float& l, float (&o)[NE]) {
     m = -INFINITY;
     l = 0.f;
@@ -135,7 +139,7 @@ __device__ __forceinline__ void chunk_partial(const float* __restrict__ qs, cons
                 const int j = min(j0 + u, 31);
                 pj[u] = j0 + u < count ? __shfl_sync(0xffffffffu, p, j) : 0.f;
                 const int rj = __shfl_sync(0xffffffffu, row, j);
-                const T* vr = v_pages + (size_t)(rj < 0 || j0 + u >= count ? safe : rj) * vd;
+                const T* vr = v_pages + (size_t)(rj < 0 || j0 + u >= count ? safe : rj) * v_ld;
 #pragma unroll
                 for (int e = 0; e < NE; ++e) {
                     const int d = e * 32 + lane;
@@ -200,7 +204,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict
                             const int* __restrict__ token_req, const int* __restrict__ positions,
                             const int* __restrict__ block_table, int max_pages, int n_tokens, int nq, int nkv, int hd,
                             int page_size, int window, float scale, float* __restrict__ scratch, int max_chunks,
-                            int vd, const float* __restrict__ sinks, float cap, int keep) {
+                            int vd, const float* __restrict__ sinks, float cap, int keep, int v_ld) {
     extern __shared__ float q_smem[];
     pdl_begin();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -227,7 +231,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict
     for (int e = 0; e < NE; ++e) o[e] = 0.f;
     for (int slot = c0; slot <= c1; ++slot) {
         float mc, lc, oc[NE];
-        chunk_partial<T, NE>(qs, k_pages, v_pages, table, nkv, kvh, hd, vd, page_size, rk.first, rk.kept, pos, row_chunk(rk, slot),
+        chunk_partial<T, NE>(qs, k_pages, v_pages, table, nkv, kvh, hd, vd, v_ld, page_size, rk.first, rk.kept, pos, row_chunk(rk, slot),
                              scale, cap, lane, mc, lc, oc);
         merge_chunk<NE>(m, l, o, mc, lc, oc);
     }
@@ -287,7 +291,7 @@ template <typename T>
 static int launch(const void* q, int q_stride, void* out, int out_stride, const void* k_pages, const void* v_pages,
                   const int* token_req, const int* positions, const int* block_table, int max_pages, int n_tokens,
                   int nq, int nkv, int hd, int page_size, int window, float scale, float* scratch, int max_chunks,
-                  int vd, const float* sinks, float cap, int keep, cudaStream_t stream) {
+                  int vd, const float* sinks, float cap, int keep, int v_ld, cudaStream_t stream) {
     const int blocks = (n_tokens * nq + WARPS - 1) / WARPS;
     const size_t smem = (size_t)WARPS * hd * sizeof(float);
     const bool split = scratch != nullptr && max_chunks > 1;
@@ -295,10 +299,10 @@ static int launch(const void* q, int q_stride, void* out, int out_stride, const 
         if (!split) \
             return wllm_launch(paged_attention_simt_kernel<T, NE, false>, blocks, WARPS * 32, smem, stream, \
                 (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pages, (const T*)v_pages, token_req, positions, \
-                block_table, max_pages, n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks, cap, keep); \
+                block_table, max_pages, n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks, cap, keep, v_ld); \
         const int st = wllm_launch(paged_attention_simt_kernel<T, NE, true>, dim3(blocks, max_chunks), WARPS * 32, smem, \
                 stream, (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pages, (const T*)v_pages, token_req, \
-                positions, block_table, max_pages, n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks, cap, keep); \
+                positions, block_table, max_pages, n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks, cap, keep, v_ld); \
         if (st != WLLM_OK) return st; \
         return wllm_launch(paged_attention_simt_merge_kernel<T, NE>, blocks, WARPS * 32, 0, stream, (T*)out, out_stride, \
                 positions, n_tokens, nq, vd, window, (const float*)scratch, max_chunks, sinks, keep); \
@@ -314,12 +318,15 @@ static int launch(const void* q, int q_stride, void* out, int out_stride, const 
 // max_chunks > 1 the split kernels run; max_chunks must be at least the number of chunks of 64 keys that any
 // row of the step touches, or the results, still right, are no longer bit-equal to the walk's.
 // vd: size of a value head (and of a head's output row); sinks: one 32-bit number per query head, or null.
-WLLM_API int wllm_paged_attention_simt_general(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+// v_ld: elements between two value rows (0: vd).
+WLLM_API int wllm_paged_attention_simt_strided(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                                                const void* v_pages, int dtype, const int* token_req, const int* positions,
                                                const int* block_table, int max_pages, int n_tokens, int nq, int nkv, int hd,
                                                int page_size, int window, float scale, float* scratch, int max_chunks,
-                                               int vd, const float* sinks, float cap, int keep, cudaStream_t stream) {
+                                               int vd, const float* sinks, float cap, int keep, int v_ld, cudaStream_t stream) {
     if (n_tokens <= 0) return WLLM_OK;
+    if (v_ld == 0) v_ld = vd;
+    if (v_ld < vd) return WLLM_BAD_SIZE;
     if (keep < 0 || cap < 0.f || (keep > 0 && window <= 0)) return WLLM_BAD_SIZE;
     // key rows are read with 16-byte loads: head sizes come in steps of 8 up to 512
     if (hd <= 0 || hd > 512 || hd % 8 != 0 || vd <= 0 || vd > 512 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 ||
@@ -329,12 +336,22 @@ WLLM_API int wllm_paged_attention_simt_general(const void* q, int q_stride, void
     if (dtype == WLLM_BF16) {
         if (q_stride % 8 != 0) return WLLM_BAD_ALIGN;
         return launch<bf16>(q, q_stride, out, out_stride, k_pages, v_pages, token_req, positions, block_table, max_pages,
-                            n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks, cap, keep, stream);
+                            n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks, cap, keep, v_ld, stream);
     }
     if (dtype == WLLM_F32)
         return launch<float>(q, q_stride, out, out_stride, k_pages, v_pages, token_req, positions, block_table, max_pages,
-                             n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks, cap, keep, stream);
+                             n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks, cap, keep, v_ld, stream);
     return WLLM_BAD_DTYPE;
+}
+
+WLLM_API int wllm_paged_attention_simt_general(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                               const void* v_pages, int dtype, const int* token_req, const int* positions,
+                                               const int* block_table, int max_pages, int n_tokens, int nq, int nkv, int hd,
+                                               int page_size, int window, float scale, float* scratch, int max_chunks,
+                                               int vd, const float* sinks, float cap, int keep, cudaStream_t stream) {
+    return wllm_paged_attention_simt_strided(q, q_stride, out, out_stride, k_pages, v_pages, dtype, token_req, positions,
+                                             block_table, max_pages, n_tokens, nq, nkv, hd, page_size, window, scale, scratch,
+                                             max_chunks, vd, sinks, cap, keep, 0, stream);
 }
 
 WLLM_API int wllm_paged_attention_simt(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
@@ -366,7 +383,7 @@ paged_attention_simt_tiled_kernel(const T* __restrict__ q, int q_stride, T* __re
                                   const int* __restrict__ req_q_start, const int* __restrict__ req_q_len,
                                   const int* __restrict__ req_ctx_len, const int* __restrict__ block_table, int max_pages,
                                   int nq, int nkv, int hd, int page_size, int window, float scale, int vd,
-                                  const float* __restrict__ sinks, float cap, int keep) {
+                                  const float* __restrict__ sinks, float cap, int keep, int v_ld) {
     constexpr int VN = Vec<T>::N;                  // elements of a 16-byte piece
     extern __shared__ __align__(16) unsigned char tl_smem[];
     pdl_begin();
@@ -415,7 +432,7 @@ paged_attention_simt_tiled_kernel(const T* __restrict__ q, int q_stride, T* __re
             size_t row = 0;
             if (valid) row = ((size_t)table[key / page_size] * nkv + g) * page_size + key % page_size;
             if (piece < kp) cp_async_16(ks + ((size_t)stage * 32 + kl) * kld + piece * VN, k_pages + row * hd + piece * VN, valid);
-            else cp_async_16(vs + ((size_t)stage * 32 + kl) * vd + (piece - kp) * VN, v_pages + row * vd + (piece - kp) * VN, valid);
+            else cp_async_16(vs + ((size_t)stage * 32 + kl) * vd + (piece - kp) * VN, v_pages + row * v_ld + (piece - kp) * VN, valid);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -530,7 +547,7 @@ template <typename T>
 static int launch_tiled(const void* q, int q_stride, void* out, int out_stride, const void* k_pages, const void* v_pages,
                         const int* req_q_start, const int* req_q_len, const int* req_ctx_len, const int* block_table,
                         int max_pages, int requests, int max_q_len, int nq, int nkv, int hd, int page_size, int window,
-                        float scale, int vd, const float* sinks, float cap, int keep, cudaStream_t stream) {
+                        float scale, int vd, const float* sinks, float cap, int keep, int v_ld, cudaStream_t stream) {
     const int rep = nq / nkv;
     const dim3 grid((max_q_len * rep + TL_ROWS - 1) / TL_ROWS, nkv, requests);
     const size_t smem = (size_t)TL_ROWS * hd * sizeof(float) + 2 * 32 * ((size_t)(hd + Vec<T>::N) + vd) * sizeof(T);
@@ -544,7 +561,7 @@ static int launch_tiled(const void* q, int q_stride, void* out, int out_stride, 
         } \
         return wllm_launch(paged_attention_simt_tiled_kernel<T, NE>, grid, TL_WARPS * 32, smem, stream, (const T*)q, q_stride, \
                            (T*)out, out_stride, (const T*)k_pages, (const T*)v_pages, req_q_start, req_q_len, req_ctx_len, \
-                           block_table, max_pages, nq, nkv, hd, page_size, window, scale, vd, sinks, cap, keep); \
+                           block_table, max_pages, nq, nkv, hd, page_size, window, scale, vd, sinks, cap, keep, v_ld); \
     } while (0)
     const int smem_max = TL_ROWS * 256 * (int)sizeof(float) + 2 * 32 * ((256 + Vec<T>::N) + 256) * (int)sizeof(T);
     if (vd <= 64) GO(2);
@@ -555,12 +572,14 @@ static int launch_tiled(const void* q, int q_stride, void* out, int out_stride, 
 
 // The tiled kernel for the requests of a step (all of them: a request with one token is a tile with few rows).
 // Head sizes up to 256; the result is the walk's bit for bit.
-WLLM_API int wllm_paged_attention_simt_tiled_general(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+WLLM_API int wllm_paged_attention_simt_tiled_strided(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                                                      const void* v_pages, int dtype, const int* req_q_start, const int* req_q_len,
                                                      const int* req_ctx_len, const int* block_table, int max_pages, int requests,
                                                      int max_q_len, int nq, int nkv, int hd, int page_size, int window, float scale,
-                                                     int vd, const float* sinks, float cap, int keep, cudaStream_t stream) {
+                                                     int vd, const float* sinks, float cap, int keep, int v_ld, cudaStream_t stream) {
     if (requests <= 0 || max_q_len <= 0) return WLLM_OK;
+    if (v_ld == 0) v_ld = vd;
+    if (v_ld < vd || v_ld % 8 != 0) return WLLM_BAD_SIZE;
     if (keep < 0 || cap < 0.f || (keep > 0 && window <= 0)) return WLLM_BAD_SIZE;
     if (hd <= 0 || hd > 256 || hd % 8 != 0 || vd <= 0 || vd > 256 || vd % 8 != 0 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || max_pages <= 0 ||
         nkv > 65535 || requests > 65535)
@@ -569,13 +588,23 @@ WLLM_API int wllm_paged_attention_simt_tiled_general(const void* q, int q_stride
         if (q_stride % 8 != 0) return WLLM_BAD_ALIGN;
         return launch_tiled<bf16>(q, q_stride, out, out_stride, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len,
                                   block_table, max_pages, requests, max_q_len, nq, nkv, hd, page_size, window, scale, vd, sinks,
-                                  cap, keep, stream);
+                                  cap, keep, v_ld, stream);
     }
     if (dtype == WLLM_F32)
         return launch_tiled<float>(q, q_stride, out, out_stride, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len,
                                    block_table, max_pages, requests, max_q_len, nq, nkv, hd, page_size, window, scale, vd, sinks,
-                                   cap, keep, stream);
+                                   cap, keep, v_ld, stream);
     return WLLM_BAD_DTYPE;
+}
+
+WLLM_API int wllm_paged_attention_simt_tiled_general(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                                     const void* v_pages, int dtype, const int* req_q_start, const int* req_q_len,
+                                                     const int* req_ctx_len, const int* block_table, int max_pages, int requests,
+                                                     int max_q_len, int nq, int nkv, int hd, int page_size, int window, float scale,
+                                                     int vd, const float* sinks, float cap, int keep, cudaStream_t stream) {
+    return wllm_paged_attention_simt_tiled_strided(q, q_stride, out, out_stride, k_pages, v_pages, dtype, req_q_start, req_q_len,
+                                                   req_ctx_len, block_table, max_pages, requests, max_q_len, nq, nkv, hd, page_size,
+                                                   window, scale, vd, sinks, cap, keep, 0, stream);
 }
 
 WLLM_API int wllm_paged_attention_simt_tiled(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,

@@ -34,6 +34,13 @@ __device__ __forceinline__ void rotate_pair(float x1, float x2, float sn, float 
     y2 = __fadd_rn(__fmul_rn(x2, cs), __fmul_rn(x1, sn));
 }
 
+// The first key that a row at position `pos` sees (it sees first .. pos).  window > 0: itself and the window - 1 keys before
+// it; window < 0: the earlier keys of its own block of -window positions, blocks counted from position 0; 0: every key.
+__host__ __device__ __forceinline__ int first_visible_key(int pos, int window) {
+    if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
+    return window < 0 ? pos - pos % (-window) : 0;
+}
+
 static inline int wllm_launch_status() {
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? WLLM_OK : 1000 + (int)e;

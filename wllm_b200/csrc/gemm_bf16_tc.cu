@@ -41,8 +41,9 @@ template <int AROWS> struct Ring {
 };
 constexpr int NUM_THREADS = 192;
 
-enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_GATED_GELU = 2, EPI_GATED_SILU = 3, EPI_GATED_RELU = 4, EPI_GATED_CAPPED = 5 };
-__host__ __device__ constexpr bool epi_gated(int e) { return e >= EPI_GATED_GELU; }
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_GATED_GELU = 2, EPI_GATED_SILU = 3, EPI_GATED_RELU = 4, EPI_GATED_CAPPED = 5,
+       EPI_RELU_SQUARED = 6 };       // the last one has no gate: bf16 C = max(A W^T, 0)^2
+__host__ __device__ constexpr bool epi_gated(int e) { return e >= EPI_GATED_GELU && e <= EPI_GATED_CAPPED; }
 // The gated epilogues' constants (EPI_GATED_CAPPED alone reads them: limit, slope), passed by value down to the drain.
 struct EpiParams { float p0, p1; };
 // With k_splits > 1 (32-bit output only) the K range is cut into k_splits parts of whole 64-column
@@ -91,7 +92,10 @@ __device__ __forceinline__ void drain_chunk(void* __restrict__ c, int ldc, int M
     } else {
         tc_wait_ld();
 #pragma unroll
-        for (int i = 0; i < W; ++i) f[i] = __uint_as_float(v[i]);
+        for (int i = 0; i < W; ++i) {
+            f[i] = __uint_as_float(v[i]);
+            if (EPI == EPI_RELU_SQUARED) { f[i] = fmaxf(f[i], 0.f); f[i] *= f[i]; }
+        }
     }
     if (row >= M) return;
     if (EPI == EPI_F32) {
@@ -771,12 +775,13 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int ldc
 // half_rows columns of the gated output (by 128 rows, or 256 rows on a pair of CTAs).  On pairs without a gate
 // it may also be a multiple of 8, or 144 to 256 in steps of 16 (wide tiles, see the pair kernel).
 // epilogue 5: the clamped gated unit g = min(gate, p0), u = clamp(up, -p0, p0), g sigmoid(p1 g) (u + 1), with its two constants.
+// epilogue 6: no gate, bf16 C [M, N] = max(A W^T, 0)^2 (the unit of a feed-forward without a gate).
 WLLM_API int wllm_gemm_bf16_tc_params(const void* a, int lda, const void* w, int ldw, void* c, int ldc, int M, int N, int K,
                                       int epilogue, int k_splits, int half_rows, int* status, int max_ctas, float p0, float p1,
                                       cudaStream_t stream) {
     const EpiParams ep{p0, p1};
     if (M <= 0 || N <= 0) return WLLM_OK;
-    if (epilogue < 0 || epilogue > EPI_GATED_CAPPED) return WLLM_BAD_SIZE;
+    if (epilogue < 0 || epilogue > EPI_RELU_SQUARED) return WLLM_BAD_SIZE;
     if (k_splits < 1 || (k_splits > 1 && epilogue != EPI_F32)) return WLLM_BAD_SIZE;
     {
         const int kblocks = (K + BK - 1) / BK, kb_per = (kblocks + k_splits - 1) / k_splits;
@@ -810,6 +815,7 @@ WLLM_API int wllm_gemm_bf16_tc_params(const void* a, int lda, const void* w, int
             case EPI_GATED_SILU: return launch_pair<EPI_GATED_SILU>(ma, mw, c, ldc, M, N, K, N / 2, 1, half_rows, status, pairs, stream);
             case EPI_GATED_RELU: return launch_pair<EPI_GATED_RELU>(ma, mw, c, ldc, M, N, K, N / 2, 1, half_rows, status, pairs, stream);
             case EPI_GATED_CAPPED: return launch_pair<EPI_GATED_CAPPED>(ma, mw, c, ldc, M, N, K, N / 2, 1, half_rows, status, pairs, stream, ep);
+            case EPI_RELU_SQUARED: return launch_pair<EPI_RELU_SQUARED>(ma, mw, c, ldc, M, N, K, 0, 1, half_rows, status, pairs, stream);
         }
         return WLLM_BAD_SIZE;
     }
@@ -822,6 +828,7 @@ WLLM_API int wllm_gemm_bf16_tc_params(const void* a, int lda, const void* w, int
         case EPI_GATED_SILU: return launch<EPI_GATED_SILU>(ma, mw, c, ldc, M, N, K, N / 2, 1, half_rows, status, ctas, stream);
         case EPI_GATED_RELU: return launch<EPI_GATED_RELU>(ma, mw, c, ldc, M, N, K, N / 2, 1, half_rows, status, ctas, stream);
         case EPI_GATED_CAPPED: return launch<EPI_GATED_CAPPED>(ma, mw, c, ldc, M, N, K, N / 2, 1, half_rows, status, ctas, stream, ep);
+        case EPI_RELU_SQUARED: return launch<EPI_RELU_SQUARED>(ma, mw, c, ldc, M, N, K, 0, 1, half_rows, status, ctas, stream);
     }
     return WLLM_BAD_SIZE;
 }

@@ -10,6 +10,8 @@
 // of squares is reduced in a fixed order that depends on nothing but the row.
 // With `center` the row's mean is taken off first (a layer norm without a bias):
 //     out[i] = (r - mean(r)) / sqrt(mean((r - mean)^2) + eps) * (offset + w)
+// Without a gain (`w` null) nothing is normed: out = r rounded to the matrix type, which is how a sublayer that reads
+// the residual as it is gets its input (the pending add is still folded in).
 // `wllm_branch_norm` norms a branch output (or two of them) that is not yet part of the residual:
 //     out = factor * (norm(a) * wa  [+ norm(b) * wb]),   32-bit out
 // which is the norm behind a sublayer of a block that norms on both sides, and the mean of two mixers.
@@ -78,13 +80,14 @@ __global__ void rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__
     pdl_launch_dependents();
     constexpr bool one_pass = VEC == 4 && VPT > 0;
     constexpr int NV = VPT > 0 ? VPT : 1;
+    const bool plain = w == nullptr;      // no gain: the row goes out as it is
     float wv[NV][4];
     if (one_pass) {          // the gain is written by no kernel: it is read while the predecessor still runs
 #pragma unroll
         for (int k = 0; k < NV; ++k) {
             const int c = (threadIdx.x + k * blockDim.x) * 4;
             wv[k][0] = wv[k][1] = wv[k][2] = wv[k][3] = 0.f;
-            if (c < H) load4(w + c, wv[k]);
+            if (c < H && !plain) load4(w + c, wv[k]);
         }
     }
     pdl_wait();
@@ -108,6 +111,17 @@ __global__ void rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__
                 for (int e = 0; e < 4; ++e) sum += v[k][e];
             }
         }
+        if (plain) {
+#pragma unroll
+            for (int k = 0; k < NV; ++k) {
+                const int c = (threadIdx.x + k * blockDim.x) * 4;
+                if (c < H) {
+                    if (write_back) store4(r + c, v[k]);
+                    store4(o + c, v[k]);
+                }
+            }
+            return;
+        }
         const float mean = center ? block_sum(sum, scratch) / (float)H : 0.f;     // (x - 0) is x, bit for bit
 #pragma unroll
         for (int k = 0; k < NV; ++k) {
@@ -129,6 +143,18 @@ __global__ void rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__
                 for (int e = 0; e < 4; ++e) y[e] = ((v[k][e] - mean) * inv) * (offset + wv[k][e]);
                 store4(o + c, y);
             }
+        }
+        return;
+    }
+    if (plain) {
+        for (int c = threadIdx.x * VEC; c < H; c += blockDim.x * VEC) {
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+            if (VEC == 4) load4(r + c, v); else v[0] = r[c];
+            if (d) add_parts<TD, VEC>(v, d + c, delta_splits, delta_split_stride);
+            if (write_back) {
+                if (VEC == 4) store4(r + c, v); else r[c] = v[0];
+            }
+            if (VEC == 4) store4(o + c, v); else o[c] = from_f32<TO>(v[0]);
         }
         return;
     }
@@ -258,7 +284,7 @@ __device__ __forceinline__ void branch_stats(const void* p, int dtype, int parts
 template <bool MULTI>
 __global__ void branch_norm_kernel(const void* __restrict__ a, int a_dtype, int a_parts, size_t a_stride, const void* __restrict__ wa,
                                    const void* __restrict__ b, int b_dtype, int b_parts, size_t b_stride, const void* __restrict__ wb,
-                                   int w_dtype, float eps, int center, float factor, float* __restrict__ out, int H) {
+                                   int w_dtype, float eps, int center, float factor, float* __restrict__ out, int H, float offset) {
     __shared__ float scratch[32];
     pdl_begin();
     const size_t row0 = (size_t)blockIdx.x * H;
@@ -266,17 +292,18 @@ __global__ void branch_norm_kernel(const void* __restrict__ a, int a_dtype, int 
     branch_stats<MULTI>(a, a_dtype, a_parts, a_stride, row0, H, center, eps, scratch, mean_a, inv_a);
     if (b) branch_stats<MULTI>(b, b_dtype, b_parts, b_stride, row0, H, center, eps, scratch, mean_b, inv_b);
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
-        float y = ((parts_at<MULTI>(a, a_dtype, a_parts, a_stride, row0 + c) - mean_a) * inv_a) * any_at(wa, w_dtype, c);
-        if (b) y += ((parts_at<MULTI>(b, b_dtype, b_parts, b_stride, row0 + c) - mean_b) * inv_b) * any_at(wb, w_dtype, c);
+        float y = ((parts_at<MULTI>(a, a_dtype, a_parts, a_stride, row0 + c) - mean_a) * inv_a) * (offset + any_at(wa, w_dtype, c));
+        if (b) y += ((parts_at<MULTI>(b, b_dtype, b_parts, b_stride, row0 + c) - mean_b) * inv_b) * (offset + any_at(wb, w_dtype, c));
         out[row0 + c] = y * factor;
     }
 }
 
 // out[n, H] (32-bit) = factor * (norm(a) * wa + norm(b) * wb); b and wb may be null.  a and b are [n, H] tensors of either
-// element type or `parts` 32-bit slabs `stride` elements apart; the gains share one element type.
-WLLM_API int wllm_branch_norm(const void* a, int a_dtype, int a_parts, long long a_stride, const void* wa,
-                              const void* b, int b_dtype, int b_parts, long long b_stride, const void* wb, int w_dtype,
-                              float eps, int center, float factor, float* out, int n, int H, cudaStream_t stream) {
+// element type or `parts` 32-bit slabs `stride` elements apart; the gains share one element type and are offset + w.
+WLLM_API int wllm_branch_norm_offset(const void* a, int a_dtype, int a_parts, long long a_stride, const void* wa,
+                                     const void* b, int b_dtype, int b_parts, long long b_stride, const void* wb, int w_dtype,
+                                     float eps, int center, float factor, float offset, float* out, int n, int H,
+                                     cudaStream_t stream) {
     if (n <= 0) return WLLM_OK;
     if (H <= 0 || a_parts < 1 || (b && b_parts < 1)) return WLLM_BAD_SIZE;
     if ((a_dtype != WLLM_BF16 && a_dtype != WLLM_F32) || (w_dtype != WLLM_BF16 && w_dtype != WLLM_F32) ||
@@ -285,17 +312,25 @@ WLLM_API int wllm_branch_norm(const void* a, int a_dtype, int a_parts, long long
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     if (a_parts > 1 || (b && b_parts > 1))
         return wllm_launch(branch_norm_kernel<true>, n, threads, 0, stream, a, a_dtype, a_parts, (size_t)a_stride, wa, b, b_dtype,
-                           b_parts, (size_t)b_stride, wb, w_dtype, eps, center ? 1 : 0, factor, out, H);
+                           b_parts, (size_t)b_stride, wb, w_dtype, eps, center ? 1 : 0, factor, out, H, offset);
     return wllm_launch(branch_norm_kernel<false>, n, threads, 0, stream, a, a_dtype, a_parts, (size_t)a_stride, wa, b, b_dtype,
-                       b_parts, (size_t)b_stride, wb, w_dtype, eps, center ? 1 : 0, factor, out, H);
+                       b_parts, (size_t)b_stride, wb, w_dtype, eps, center ? 1 : 0, factor, out, H, offset);
+}
+
+WLLM_API int wllm_branch_norm(const void* a, int a_dtype, int a_parts, long long a_stride, const void* wa,
+                              const void* b, int b_dtype, int b_parts, long long b_stride, const void* wb, int w_dtype,
+                              float eps, int center, float factor, float* out, int n, int H, cudaStream_t stream) {
+    return wllm_branch_norm_offset(a, a_dtype, a_parts, a_stride, wa, b, b_dtype, b_parts, b_stride, wb, w_dtype, eps, center,
+                                   factor, 0.f, out, n, H, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------
 // A block that norms behind its sublayers as well as in front, in one kernel a row:
 //     u   = a                                             (one branch), or
 //           factor * (rms(a) * wa + rms(b) * wb)          (two mixers side by side, each normed over the width)
-//     r  += norm_p(u) * wp                                (the norm behind the sublayer; center_p: layer norm)
-//     out = norm(r) * (offset + w)                        (the norm in front of the next sublayer, or the model's last)
+//     r  += norm_p(u) * (offset_p + wp)                   (the norm behind the sublayer; center_p: layer norm)
+//     out = norm(r) * (offset + w)                        (the norm in front of the next sublayer, or the model's last;
+//                                                          w null: out = r, for a sublayer that reads the residual as it is)
 // The row lives in shared memory between the passes (H floats); every sum is a block sum in a fixed order.
 // With `rows` the residual is read at rows[i] and left as it is (the last norm at the places whose logits are wanted).
 // ---------------------------------------------------------------------------------------------------
@@ -305,7 +340,7 @@ __global__ void sandwich_norm_kernel(float* __restrict__ resid, const void* __re
                                      size_t b_stride, const void* __restrict__ wb, float inner_eps, float factor,
                                      const void* __restrict__ wp, int center_p, float eps_p, const void* __restrict__ w,
                                      float offset, int center, float eps, int w_dtype, TO* __restrict__ out,
-                                     const int* __restrict__ rows, int H) {
+                                     const int* __restrict__ rows, int H, float offset_p) {
     extern __shared__ float row_s[];          // [H] the row between the passes; with two branches [H] more for the second
     __shared__ float scratch[32];
     pdl_begin();
@@ -342,27 +377,32 @@ __global__ void sandwich_norm_kernel(float* __restrict__ resid, const void* __re
     float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)H + eps_p);
     sum = 0.f;
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
-        const float x = resid[row0 + c] + ((row_s[c] - mean) * inv) * any_at(wp, w_dtype, c);
+        const float x = resid[row0 + c] + ((row_s[c] - mean) * inv) * (offset_p + any_at(wp, w_dtype, c));
         if (!rows) resid[row0 + c] = x;
         row_s[c] = x;
         sum += x;
+    }
+    TO* o = out + (size_t)i * H;
+    if (w == nullptr) {           // every thread reads back what it wrote itself
+        for (int c = threadIdx.x; c < H; c += blockDim.x) o[c] = from_f32<TO>(row_s[c]);
+        return;
     }
     mean = center ? block_sum(sum, scratch) / (float)H : 0.f;
     ss = 0.f;
     for (int c = threadIdx.x; c < H; c += blockDim.x) ss += (row_s[c] - mean) * (row_s[c] - mean);
     inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)H + eps);
-    TO* o = out + (size_t)i * H;
     for (int c = threadIdx.x; c < H; c += blockDim.x)
         o[c] = from_f32<TO>(((row_s[c] - mean) * inv) * (offset + any_at(w, w_dtype, c)));
 }
 
 // a, b: branch outputs [n, H] of either element type, or `parts` 32-bit slabs `stride` elements apart; wa null: a is taken as
 // it is (b, wb unused); all gains (wa, wb, wp, w) share one element type.
-WLLM_API int wllm_sandwich_norm(float* resid, const void* a, int a_dtype, int a_parts, long long a_stride, const void* wa,
-                                const void* b, int b_dtype, int b_parts, long long b_stride, const void* wb, float inner_eps,
-                                float factor, const void* wp, int center_p, float eps_p, const void* w, float offset, int center,
-                                float eps, int w_dtype, void* out, int out_dtype, const int* rows, int n, int H,
-                                cudaStream_t stream) {
+// offset_p: the gain of the norm behind the sublayer is offset_p + wp; w null: the second norm is left out (out = r).
+WLLM_API int wllm_sandwich_norm_offset(float* resid, const void* a, int a_dtype, int a_parts, long long a_stride, const void* wa,
+                                       const void* b, int b_dtype, int b_parts, long long b_stride, const void* wb, float inner_eps,
+                                       float factor, const void* wp, float offset_p, int center_p, float eps_p, const void* w,
+                                       float offset, int center, float eps, int w_dtype, void* out, int out_dtype,
+                                       const int* rows, int n, int H, cudaStream_t stream) {
     if (n <= 0) return WLLM_OK;
     if (H <= 0 || H > 24 * 1024 || a_parts < 1 || (b && b_parts < 1) || (b && !wa)) return WLLM_BAD_SIZE;
     if ((a_dtype != WLLM_BF16 && a_dtype != WLLM_F32) || (w_dtype != WLLM_BF16 && w_dtype != WLLM_F32) ||
@@ -383,11 +423,21 @@ WLLM_API int wllm_sandwich_norm(float* resid, const void* a, int a_dtype, int a_
     const bool multi = a_parts > 1 || (b && b_parts > 1);
 #define GO2(TO, M) wllm_launch(sandwich_norm_kernel<TO, M>, n, threads, smem, stream, resid, a, a_dtype, a_parts, (size_t)a_stride, wa, b, \
         b_dtype, b_parts, (size_t)b_stride, wb, inner_eps, factor, wp, center_p ? 1 : 0, eps_p, w, offset, center ? 1 : 0, eps, \
-        w_dtype, (TO*)out, rows, H)
+        w_dtype, (TO*)out, rows, H, offset_p)
 #define GO(TO) (multi ? GO2(TO, true) : GO2(TO, false))
     if (out_dtype == WLLM_BF16) return GO(bf16);
     if (out_dtype == WLLM_F32) return GO(float);
 #undef GO
 #undef GO2
     return WLLM_BAD_DTYPE;
+}
+
+WLLM_API int wllm_sandwich_norm(float* resid, const void* a, int a_dtype, int a_parts, long long a_stride, const void* wa,
+                                const void* b, int b_dtype, int b_parts, long long b_stride, const void* wb, float inner_eps,
+                                float factor, const void* wp, int center_p, float eps_p, const void* w, float offset, int center,
+                                float eps, int w_dtype, void* out, int out_dtype, const int* rows, int n, int H,
+                                cudaStream_t stream) {
+    if (w == nullptr) return WLLM_BAD_SIZE;
+    return wllm_sandwich_norm_offset(resid, a, a_dtype, a_parts, a_stride, wa, b, b_dtype, b_parts, b_stride, wb, inner_eps, factor,
+                                     wp, 0.f, center_p, eps_p, w, offset, center, eps, w_dtype, out, out_dtype, rows, n, H, stream);
 }

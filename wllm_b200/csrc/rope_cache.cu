@@ -14,6 +14,9 @@
 // of vd.  With `unit_norm` every rotated query and key head is divided by its root mean square,
 // y / sqrt(mean(y^2) + norm_eps), in 32-bit, before it is rounded and stored.
 //
+// With row gains (`wllm_rope_row_norm_kv_write`) the query row and the key row of a token are normed as wholes, all heads at
+// once, in front of the turn: q <- q / sqrt(mean(q^2) + eps) * wq over the token's nq * hd query elements, the same for k.
+//
 // Page layout: [page][kv_head][slot_in_page][head_dim] (values: [..][vd]); `slots[n]` is page * page_size + slot_in_page.
 #include "common.cuh"
 
@@ -332,6 +335,119 @@ __global__ void rope_kv_write_rows_kernel(const bf16* __restrict__ qkv, int row_
         else { const int v = item - rotated * tail; h = rotated + v / whole; c = (v % whole) * 8; }
         *reinterpret_cast<uint4*>(dst_of(h) + c) = *reinterpret_cast<const uint4*>(row + (size_t)h * hd + c);
     }
+}
+
+// The query row and the key row of a token normed as wholes in front of the turn.  One CTA a token: the row's q and k parts
+// (partial sums added in slab order) go to shared memory with their sums of squares (block sums in a fixed order, so a
+// token's result does not depend on the step), then every thread turns pairs of the normed, gained elements.  The means
+// divide by q_count and k_count (heads that are held in steps of 8 elements carry zeros behind them, which count for nothing).
+__device__ __forceinline__ float gain_at(const void* p, int dtype, int i) {
+    return dtype == WLLM_BF16 ? __bfloat162float(reinterpret_cast<const bf16*>(p)[i]) : reinterpret_cast<const float*>(p)[i];
+}
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256)
+rope_row_norm_kernel(const TI* __restrict__ qkv, int row_stride, int in_splits, size_t in_split_stride,
+                     TO* __restrict__ q_out, int q_stride, const int* __restrict__ positions,
+                     const int* __restrict__ slots, const float* __restrict__ inv_freq,
+                     TO* __restrict__ k_pages, TO* __restrict__ v_pages, int nq, int nkv, int hd,
+                     int rot_dim, int page_size, int interleaved, int vd, const void* __restrict__ wq,
+                     const void* __restrict__ wk, int w_dtype, int q_count, int k_count, float eps) {
+    extern __shared__ float row[];            // [(nq + nkv) * hd] the token's q and k parts, [half] sines, [half] cosines
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int slot = slots ? slots[t] : -1;
+    const float pos = (float)positions[t];
+    const int half = rot_dim >> 1, qw = nq * hd, kw = nkv * hd;
+    float* sn = row + qw + kw;
+    float* cs = sn + half;
+    for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf(pos * inv_freq[j], &sn[j], &cs[j]);
+    pdl_wait();
+    const TI* x = qkv + (size_t)t * row_stride;
+    auto in = [&](int c) {     // part 0 + part 1 + ... in order; sixteen loads are in flight at a time
+        if (in_splits == 1) return to_f32(x[c]);
+        float v = 0.f;
+        for (int sp = 0; sp < in_splits; sp += 16) {
+            float part[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) part[u] = sp + u < in_splits ? to_f32(x[(size_t)(sp + u) * in_split_stride + c]) : 0.f;
+#pragma unroll
+            for (int u = 0; u < 16; ++u)
+                if (sp + u < in_splits) v = (sp + u == 0) ? part[u] : v + part[u];
+        }
+        return v;
+    };
+    float ssq = 0.f, ssk = 0.f;
+    for (int c = threadIdx.x; c < qw + kw; c += blockDim.x) {
+        const float v = in(c);
+        row[c] = v;
+        if (c < qw) ssq += v * v; else ssk += v * v;
+    }
+    ssq = block_sum(ssq, scratch);
+    ssk = block_sum(ssk, scratch);
+    const float inv_q = 1.0f / sqrtf(ssq / (float)q_count + eps);
+    const float inv_k = kw > 0 ? 1.0f / sqrtf(ssk / (float)k_count + eps) : 0.f;
+    const int heads = slot < 0 ? nq : nq + nkv;
+    auto dst_of = [&](int h) -> TO* {
+        if (h < nq) return q_out + (size_t)t * q_stride + (size_t)h * hd;
+        return k_pages + (((size_t)(slot / page_size) * nkv + (h - nq)) * page_size + slot % page_size) * hd;
+    };
+    auto normed = [&](int h, int c) {     // element c of head h, normed and gained
+        return h < nq ? (row[h * hd + c] * inv_q) * gain_at(wq, w_dtype, h * hd + c)
+                      : (row[h * hd + c] * inv_k) * gain_at(wk, w_dtype, (h - nq) * hd + c);
+    };
+    for (int item = threadIdx.x; item < heads * half; item += blockDim.x) {
+        const int h = item / half, j = item % half;
+        const int ia = interleaved ? 2 * j : j, ib = interleaved ? 2 * j + 1 : j + half;
+        float y1, y2;
+        rotate_pair(normed(h, ia), normed(h, ib), sn[j], cs[j], y1, y2);
+        TO* dst = dst_of(h);
+        dst[ia] = from_f32<TO>(y1);
+        dst[ib] = from_f32<TO>(y2);
+    }
+    const int rest = hd - rot_dim;
+    for (int item = threadIdx.x; item < heads * rest; item += blockDim.x) {
+        const int h = item / rest, c = rot_dim + item % rest;
+        dst_of(h)[c] = from_f32<TO>(normed(h, c));
+    }
+    if (slot < 0) return;
+    for (int item = threadIdx.x; item < nkv * vd; item += blockDim.x) {
+        const int kvh = item / vd, c = item % vd;
+        v_pages[(((size_t)(slot / page_size) * nkv + kvh) * page_size + slot % page_size) * vd + c] = from_f32<TO>(in(qw + kw + item));
+    }
+}
+
+// wq [nq * hd], wk [nkv * hd]: the gains of the two row norms (one element type); q_count, k_count: the elements that
+// count for the means (nq * hd and nkv * hd unless the heads are held with zeros behind them).
+WLLM_API int wllm_rope_row_norm_kv_write(const void* qkv, int in_dtype, int row_stride, int in_splits, long long in_split_stride,
+                                         void* q_out, int out_dtype, int q_stride, const int* positions, const int* slots,
+                                         const float* inv_freq, void* k_pages, void* v_pages, int n, int nq, int nkv, int hd,
+                                         int rot_dim, int page_size, int interleaved, int vd, const void* wq, const void* wk,
+                                         int w_dtype, int q_count, int k_count, float eps, cudaStream_t stream) {
+    if (n <= 0) return WLLM_OK;
+    if (hd <= 0 || vd <= 0 || rot_dim < 0 || rot_dim > hd || (rot_dim & 1) || page_size <= 0 || nq <= 0 || nkv < 0 ||
+        (nkv == 0 && slots != nullptr) || in_splits < 1 || q_count <= 0 || (nkv > 0 && k_count <= 0) || wq == nullptr ||
+        (nkv > 0 && wk == nullptr))
+        return WLLM_BAD_SIZE;
+    if (w_dtype != WLLM_BF16 && w_dtype != WLLM_F32) return WLLM_BAD_DTYPE;
+    const size_t smem = ((size_t)(nq + nkv) * hd + rot_dim) * sizeof(float);
+    if (smem > 200 * 1024) return WLLM_BAD_SIZE;
+#define RN(TI, TO) do { \
+        static bool raised = false; \
+        if (!raised && smem > 48 * 1024) { \
+            const cudaError_t e = cudaFuncSetAttribute(rope_row_norm_kernel<TI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+            if (e != cudaSuccess) return 1000 + (int)e; \
+            raised = true; \
+        } \
+        return wllm_launch(rope_row_norm_kernel<TI, TO>, n, 256, smem, stream, (const TI*)qkv, row_stride, in_splits, \
+            (size_t)in_split_stride, (TO*)q_out, q_stride, positions, slots, inv_freq, (TO*)k_pages, (TO*)v_pages, nq, nkv, hd, \
+            rot_dim, page_size, interleaved, vd, wq, wk, w_dtype, q_count, k_count, eps); \
+    } while (0)
+    if (in_dtype == WLLM_BF16 && out_dtype == WLLM_BF16) RN(bf16, bf16);
+    if (in_dtype == WLLM_F32 && out_dtype == WLLM_BF16) RN(float, bf16);
+    if (in_dtype == WLLM_F32 && out_dtype == WLLM_F32) RN(float, float);
+#undef RN
+    return WLLM_BAD_DTYPE;
 }
 
 // vd: size of a value head (hd when they are the same); unit_norm: divide rotated q and k heads by their root mean square.

@@ -56,7 +56,10 @@ class ComposedModel:
                             raise TypeError(f"a run that reads the cache of run {i} has other key/value heads than it")
                         window = None if window is None or other.window is None else max(window, other.window)
                         keep = max(keep, other.keep_first)
-                    key = (one.kv_heads, one.head_dim, window, vd, keep if window is not None else 0)
+                    if (one.blocks or one.values_in_keys) and readers.get(i):
+                        raise TypeError(f"run {i}: a cache of blocks or of values held in the keys' rows is read by its own run alone")
+                    key = (one.kv_heads, one.head_dim, window, vd, keep if window is not None else 0,
+                           bool(one.blocks) and window is not None, bool(one.values_in_keys))
                     if key not in keys:
                         keys.append(key)
                         layers.append(0)
@@ -72,10 +75,10 @@ class ComposedModel:
                     raise TypeError(f"run {i}: cache_need() returned {one!r}; expected KVNeed, StateNeed, None or a tuple of them")
             refs.append(ref)
         groups = []
-        for (kvh, hd, window, vd, keep), n in zip(keys, layers):
-            name = ("all" if window is None else f"window{window}") + (f"+first{keep}" if keep else "") + f"-{kvh}x{hd}" + \
-                (f"v{vd}" if vd else "")
-            groups.append(CacheGroupSpec(name, n, kvh, hd, window, vd, keep))
+        for (kvh, hd, window, vd, keep, blocks, inside), n in zip(keys, layers):
+            name = ("all" if window is None else f"{'blocks' if blocks else 'window'}{window}") + (f"+first{keep}" if keep else "") + \
+                f"-{kvh}x{hd}" + (f"v{vd}" if vd else "") + ("-in-keys" if inside else "")
+            groups.append(CacheGroupSpec(name, n, kvh, hd, window, vd, keep, blocks, inside))
         return groups, states, refs
 
     # -- weights -------------------------------------------------------------------

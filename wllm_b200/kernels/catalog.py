@@ -13,6 +13,7 @@ FAMILIES = {
     "attention_simt": [{}],
     "activation": [{}],
     "linear_attention": [{}],
+    "latent_attention": [{}],
     "hyper_connections": [{}],
     "moe": [{}],
     "gemm_f32": [{}],

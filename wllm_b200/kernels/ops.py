@@ -119,16 +119,17 @@ def patch_tokens(ids: torch.Tensor, dst: torch.Tensor, sampled: torch.Tensor, sr
                                  _ptr(_int32(src, "src")), n, _stream()), "patch_tokens")
 
 
-def rmsnorm(resid: torch.Tensor, delta, weight: torch.Tensor, eps: float, offset: float, out: torch.Tensor,
+def rmsnorm(resid: torch.Tensor, delta, weight, eps: float, offset: float, out: torch.Tensor,
             rows=None, delta_splits: int = 0, center: bool = False) -> torch.Tensor:
     """Fold `delta` into the residual (when given), then norm: see csrc/norm.cu.  With `delta_splits` = S > 0,
     `delta` is [S, n, H] float32 partial sums that are added in order.  `center`: the row's mean is taken off
-    first (a layer norm without a bias)."""
+    first (a layer norm without a bias).  `weight` None: nothing is normed, `out` is the residual's rows rounded to
+    its element type."""
     _need_cuda(resid, delta, weight, out, rows)
     H = resid.shape[1]
     n = rows.shape[0] if rows is not None else resid.shape[0]
     assert resid.dtype == torch.float32 and resid.is_contiguous() and out.is_contiguous() and out.shape == (n, H)
-    assert weight.shape == (H,) and weight.is_contiguous()
+    assert weight is None or (weight.shape == (H,) and weight.is_contiguous())
     split_stride = 0
     if delta is not None:
         assert delta.is_contiguous()
@@ -139,7 +140,7 @@ def rmsnorm(resid: torch.Tensor, delta, weight: torch.Tensor, eps: float, offset
             assert delta.shape == resid.shape
     lib = load_family("norm")
     _check(lib.wllm_norm(_ptr(resid), _ptr(delta), _dt(delta) if delta is not None else _F32, max(1, delta_splits),
-                         ctypes.c_longlong(split_stride), _ptr(weight), _dt(weight), c_float(eps), c_float(offset),
+                         ctypes.c_longlong(split_stride), _ptr(weight), _dt(weight) if weight is not None else _F32, c_float(eps), c_float(offset),
                          1 if center else 0, _ptr(out), _dt(out), _ptr(_int32(rows, "rows") if rows is not None else None),
                          n, H, _stream()), "norm")
     return out
@@ -155,9 +156,9 @@ def _branch_args(branch, n: int, H: int):
 
 
 def branch_norm(a, weight_a: torch.Tensor, out: torch.Tensor, eps: float, center: bool = False, factor: float = 1.0,
-                b=None, weight_b: torch.Tensor | None = None) -> torch.Tensor:
-    """out[n, H] (float32) = factor * (norm(a) * weight_a [+ norm(b) * weight_b]) for branch outputs that are not part
-    of the residual yet.  `a`, `b`: (tensor [n, H] or float32 partial sums [S, n, H], S or 0), as ops.project returns
+                b=None, weight_b: torch.Tensor | None = None, offset: float = 0.0) -> torch.Tensor:
+    """out[n, H] (float32) = factor * (norm(a) * (offset + weight_a) [+ norm(b) * (offset + weight_b)]) for branch outputs
+    that are not part of the residual yet.  `a`, `b`: (tensor [n, H] or float32 partial sums [S, n, H], S or 0), as ops.project returns
     them.  `center`: layer norm without a bias, else root mean square (csrc/norm.cu)."""
     n, H = out.shape
     _need_cuda(a[0], weight_a, out, b[0] if b is not None else None, weight_b)
@@ -169,17 +170,18 @@ def branch_norm(a, weight_a: torch.Tensor, out: torch.Tensor, eps: float, center
     else:
         pb = (_ptr(None), _F32, 1, ctypes.c_longlong(0))
     lib = load_family("norm")
-    _check(lib.wllm_branch_norm(*pa, _ptr(weight_a), *pb, _ptr(weight_b), _dt(weight_a), c_float(eps), 1 if center else 0,
-                                c_float(factor), _ptr(out), n, H, _stream()), "branch_norm")
+    _check(lib.wllm_branch_norm_offset(*pa, _ptr(weight_a), *pb, _ptr(weight_b), _dt(weight_a), c_float(eps), 1 if center else 0,
+                                       c_float(factor), c_float(offset), _ptr(out), n, H, _stream()), "branch_norm")
     return out
 
 
 def sandwich_norm(resid: torch.Tensor, a, out: torch.Tensor, post_weight: torch.Tensor, post_center: bool, post_eps: float,
-                  weight: torch.Tensor, offset: float, center: bool, eps: float, rows=None, gain_a=None, b=None, gain_b=None,
-                  inner_eps: float = 0.0, factor: float = 1.0) -> torch.Tensor:
+                  weight, offset: float, center: bool, eps: float, rows=None, gain_a=None, b=None, gain_b=None,
+                  inner_eps: float = 0.0, factor: float = 1.0, post_offset: float = 0.0) -> torch.Tensor:
     """One kernel for a block that norms behind its sublayers too (csrc/norm.cu):
         u = a, or factor * (rms(a) * gain_a + rms(b) * gain_b) when gain_a is given;
-        resid += norm(u) * post_weight  (post_center: with the mean taken off);  out = norm(resid) * (offset + weight).
+        resid += norm(u) * (post_offset + post_weight)  (post_center: with the mean taken off);
+        out = norm(resid) * (offset + weight), or, with `weight` None, resid as it is (rounded to out's type).
     `a`, `b`: (tensor [n, H] or float32 partial sums [S, n, H], S or 0).  With `rows` the residual is read at those rows
     and left as it is."""
     N, H = resid.shape
@@ -187,14 +189,15 @@ def sandwich_norm(resid: torch.Tensor, a, out: torch.Tensor, post_weight: torch.
     _need_cuda(resid, a[0], out, post_weight, weight, rows, gain_a, gain_b, b[0] if b is not None else None)
     assert resid.dtype == torch.float32 and resid.is_contiguous() and out.is_contiguous() and out.shape == (n, H)
     gains = [g for g in (post_weight, weight, gain_a, gain_b) if g is not None]
-    assert all(g.shape == (H,) and g.is_contiguous() and g.dtype == weight.dtype for g in gains)
+    assert all(g.shape == (H,) and g.is_contiguous() and g.dtype == post_weight.dtype for g in gains)
     pa = _branch_args(a, N, H)
     pb = _branch_args(b, N, H) if b is not None else (_ptr(None), _F32, 1, ctypes.c_longlong(0))
     lib = load_family("norm")
-    _check(lib.wllm_sandwich_norm(_ptr(resid), *pa, _ptr(gain_a), *pb, _ptr(gain_b), c_float(inner_eps), c_float(factor),
-                                  _ptr(post_weight), 1 if post_center else 0, c_float(post_eps), _ptr(weight), c_float(offset),
-                                  1 if center else 0, c_float(eps), _dt(weight), _ptr(out), _dt(out),
-                                  _ptr(_int32(rows, "rows") if rows is not None else None), n, H, _stream()), "sandwich_norm")
+    _check(lib.wllm_sandwich_norm_offset(_ptr(resid), *pa, _ptr(gain_a), *pb, _ptr(gain_b), c_float(inner_eps), c_float(factor),
+                                         _ptr(post_weight), c_float(post_offset), 1 if post_center else 0, c_float(post_eps),
+                                         _ptr(weight), c_float(offset), 1 if center else 0, c_float(eps), _dt(post_weight),
+                                         _ptr(out), _dt(out), _ptr(_int32(rows, "rows") if rows is not None else None), n, H,
+                                         _stream()), "sandwich_norm")
     return out
 
 def hyper_norm(src: torch.Tensor, dst: torch.Tensor, S: int, branch, prev_mix, prev_out, in_w, gain: torch.Tensor, eps: float,
@@ -259,6 +262,74 @@ def rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, positions: torch.Tenso
            "rope_kv_write")
 
 
+def rope_row_norm_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor, slots, inv_freq: torch.Tensor,
+                           k_pages, v_pages, nq: int, nkv: int, hd: int, rot_dim: int, page_size: int, q_gain: torch.Tensor,
+                           k_gain: torch.Tensor, eps: float, q_count: int, k_count: int, in_splits: int = 0,
+                           pairing: str = "half", vd: int | None = None) -> None:
+    """As rope_kv_write, with the token's query row and key row normed as wholes (all heads at once) in front of the
+    turn: q <- q / sqrt(mean(q^2) + eps) * q_gain over the nq * hd query elements, the same for k with k_gain
+    (csrc/rope_cache.cu).  `q_count`, `k_count`: the elements that count for the means (heads held in steps of 8
+    elements carry zeros behind them)."""
+    if pairing not in ("half", "interleaved"):
+        raise KernelError(f"rotary pairing {pairing!r} not supported (half, interleaved)")
+    _need_cuda(qkv, q_out, positions, slots, inv_freq, k_pages, v_pages, q_gain, k_gain)
+    vd = hd if vd is None else vd
+    width = (nq + nkv) * hd + nkv * vd
+    ptr, dt, row_stride, nparts, part_stride, n = _fused_args(qkv, in_splits)
+    assert qkv.shape[-1] >= width and q_out.shape == (n, nq * hd) and q_out.stride(1) == 1
+    assert inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dim // 2 and inv_freq.is_contiguous()
+    assert q_gain.shape == (nq * hd,) and k_gain.shape == (nkv * hd,) and q_gain.dtype == k_gain.dtype
+    assert q_gain.is_contiguous() and k_gain.is_contiguous()
+    if slots is not None:
+        assert k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == q_out.dtype == v_pages.dtype
+    lib = load_family("rope_cache")
+    _check(lib.wllm_rope_row_norm_kv_write(ptr, dt, row_stride, nparts, part_stride, _ptr(q_out), _dt(q_out), q_out.stride(0),
+                                           _ptr(_int32(positions, "positions")),
+                                           _ptr(_int32(slots, "slots") if slots is not None else None), _ptr(inv_freq),
+                                           _ptr(k_pages), _ptr(v_pages), n, nq, nkv, hd, rot_dim, page_size,
+                                           1 if pairing == "interleaved" else 0, vd, _ptr(q_gain), _ptr(k_gain), _dt(q_gain),
+                                           q_count, k_count, c_float(eps), _stream()), "rope_row_norm_kv_write")
+
+
+def latent_prepare(fused: torch.Tensor, parts: int, positions: torch.Tensor, slots, inv_freq: torch.Tensor, gain: torch.Tensor,
+                   eps: float, pages: torch.Tensor, page_size: int, q_plain: torch.Tensor, q_mapped: torch.Tensor, heads: int,
+                   dim: int, rot: int, rot_dims: int, rank: int, hd: int, pairing: str = "half") -> None:
+    """From the fused projection row [heads * (dim + rot) | rank + rot] of every token (csrc/latent_attention.cu): the
+    cache row [rms(latent columns) * gain | the rot columns behind them, turned | zeros] into `pages` at `slots`; the
+    queries' plain parts into `q_plain` [n, heads * dim]; their turned parts into columns rank .. of every head of
+    `q_mapped` [n, heads * hd].  Norm and turn are 32-bit, from the projection's partial sums where it left them."""
+    if pairing not in ("half", "interleaved"):
+        raise KernelError(f"rotary pairing {pairing!r} not supported (half, interleaved)")
+    _need_cuda(fused, positions, slots, inv_freq, gain, pages, q_plain, q_mapped)
+    ptr, dt, row_stride, nparts, part_stride, n = _fused_args(fused, parts)
+    assert fused.shape[-1] >= heads * (dim + rot) + rank + rot and hd >= rank + rot
+    assert q_plain.shape == (n, heads * dim) and q_plain.is_contiguous() and q_mapped.shape == (n, heads * hd) and q_mapped.is_contiguous()
+    assert q_plain.dtype == q_mapped.dtype == pages.dtype and pages.is_contiguous() and pages.shape[-1] == hd and pages.shape[-3] == 1
+    assert gain.shape == (rank,) and gain.is_contiguous()
+    assert inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dims // 2 and inv_freq.is_contiguous()
+    lib = load_family("latent_attention")
+    _check(lib.wllm_latent_prepare(ptr, dt, row_stride, nparts, part_stride, _ptr(_int32(positions, "positions")),
+                                   _ptr(_int32(slots, "slots") if slots is not None else None), _ptr(inv_freq), _ptr(gain),
+                                   _dt(gain), c_float(eps), _ptr(pages), page_size, _ptr(q_plain), _ptr(q_mapped), _dt(q_plain),
+                                   n, heads, dim, rot, rot_dims, 1 if pairing == "interleaved" else 0, rank, hd, _stream()),
+           "latent_prepare")
+
+
+def head_linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    """y[t, h, :] = x[t, h, :] @ w[h]^T for every head h.  x [n, heads, K] and y [n, heads, N] may be views (free row and
+    head strides, unit inner stride); w [heads, N, K] contiguous.  32-bit accumulation, every output one ascending chain
+    over K (csrc/latent_attention.cu)."""
+    _need_cuda(x, w, y)
+    n, heads, K = x.shape
+    N = w.shape[1]
+    assert w.shape == (heads, N, K) and w.is_contiguous() and y.shape == (n, heads, N)
+    assert x.stride(2) == 1 and y.stride(2) == 1 and x.dtype == w.dtype == y.dtype
+    lib = load_family("latent_attention")
+    _check(lib.wllm_head_linear(_ptr(x), x.stride(0), x.stride(1), _ptr(w), _ptr(y), y.stride(0), y.stride(1), _dt(x), n, heads,
+                                N, K, _stream()), f"head_linear({n}x{heads}x{N}x{K})")
+    return y
+
+
 SIMT_CHUNK = 64    # keys per chunk of the one-warp-per-row attention (csrc/attention_simt.cu)
 
 
@@ -266,6 +337,8 @@ def simt_chunks(max_ctx: int, window: int, keep: int = 0) -> int:
     """Upper bound of the chunks of 64 keys that a row of a step touches, from the longest context of the
     step (and the window, if the layer has one, with the first keys it keeps behind it)."""
     most = -(-max(1, max_ctx) // SIMT_CHUNK)
+    if window < 0:          # a mask of blocks of -window positions: a row sees no further back than its block's start
+        return min(most, -(window // SIMT_CHUNK) + 1)
     return min(most, -(-window // SIMT_CHUNK) + 1 + -(-keep // SIMT_CHUNK)) if window > 0 else most
 
 
@@ -273,8 +346,12 @@ def paged_attention_simt(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tens
                          token_req: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor,
                          nq: int, nkv: int, hd: int, page_size: int, window: int, scale: float,
                          scratch: torch.Tensor | None = None, max_chunks: int = 0, vd: int | None = None,
-                         sinks: torch.Tensor | None = None, cap: float = 0.0, keep: int = 0) -> torch.Tensor:
+                         sinks: torch.Tensor | None = None, cap: float = 0.0, keep: int = 0,
+                         values_in_keys: bool = False) -> torch.Tensor:
     """q: [n, nq*hd] view (row stride free); pages: [num_pages, nkv, page_size, hd]; out: [n, nq*hd].
+    `window` > 0: a row sees itself and the window - 1 keys before it; < 0: the earlier keys of its own block of -window
+    positions (blocks counted from position 0); 0: every earlier key.  `values_in_keys`: a token's value is the first vd
+    elements of its key's row (`v_pages` is `k_pages`).
     `vd`: size of a value head when it is not hd (value pages [.., vd], out [n, nq*vd]); `sinks`: float32 [nq], one
     more term e^(sink) in every row's softmax denominator.  `cap` > 0: scores become cap * tanh(score / cap);
     `keep` > 0 (with a window): the sequence's first `keep` keys stay visible behind the window.
@@ -286,18 +363,20 @@ def paged_attention_simt(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tens
     vd = hd if vd is None else vd
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_pages.dtype == v_pages.dtype
     assert k_pages.is_contiguous() and v_pages.is_contiguous() and block_table.dim() == 2
-    assert k_pages.shape[-1] == hd and v_pages.shape[-1] == vd
+    assert k_pages.shape[-1] == hd and v_pages.shape[-1] == (hd if values_in_keys else vd)
+    assert not values_in_keys or (v_pages.data_ptr() == k_pages.data_ptr() and vd <= hd)
     assert sinks is None or (sinks.dtype == torch.float32 and sinks.shape == (nq,) and sinks.is_contiguous())
     if scratch is not None:
         assert scratch.dtype == torch.float32 and scratch.is_contiguous() and max_chunks >= 1
         assert scratch.numel() >= n * nq * max_chunks * (vd + 2)
     lib = load_family("attention_simt")
-    _check(lib.wllm_paged_attention_simt_general(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages),
+    _check(lib.wllm_paged_attention_simt_strided(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages),
                                                  _dt(q), _ptr(_int32(token_req, "token_req")),
                                                  _ptr(_int32(positions, "positions")), _ptr(_int32(block_table, "block_table")),
                                                  block_table.shape[1], n, nq, nkv, hd, page_size, window, c_float(scale),
                                                  _ptr(scratch), max_chunks if scratch is not None else 0, vd, _ptr(sinks),
-                                                 c_float(cap), keep, _stream()), f"paged_attention_simt(head_dim={hd}/{vd}, heads={nq}/{nkv})")
+                                                 c_float(cap), keep, hd if values_in_keys else 0, _stream()),
+           f"paged_attention_simt(head_dim={hd}/{vd}, heads={nq}/{nkv})")
     if scratch is not None and max_chunks > 1:
         global launches
         launches += 1    # the merge kernel
@@ -308,7 +387,8 @@ def paged_attention_simt_tiled(q: torch.Tensor, out: torch.Tensor, k_pages: torc
                                req_q_start: torch.Tensor, req_q_len: torch.Tensor, req_ctx_len: torch.Tensor,
                                block_table: torch.Tensor, max_q_len: int, nq: int, nkv: int, hd: int, page_size: int,
                                window: int, scale: float, vd: int | None = None,
-                               sinks: torch.Tensor | None = None, cap: float = 0.0, keep: int = 0) -> torch.Tensor:
+                               sinks: torch.Tensor | None = None, cap: float = 0.0, keep: int = 0,
+                               values_in_keys: bool = False) -> torch.Tensor:
     """The same attention as `paged_attention_simt`, bit for bit, for steps that bring portions of prompts: a CTA
     takes 32 rows of one (request, key/value head) and reads every tile of keys and values once for all of them
     (csrc/attention_simt.cu, tiled).  Head sizes up to 256; requests are given by their start, length and context."""
@@ -316,16 +396,18 @@ def paged_attention_simt_tiled(q: torch.Tensor, out: torch.Tensor, k_pages: torc
     vd = hd if vd is None else vd
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_pages.dtype == v_pages.dtype
     assert k_pages.is_contiguous() and v_pages.is_contiguous() and block_table.dim() == 2
-    assert k_pages.shape[-1] == hd and v_pages.shape[-1] == vd
+    assert k_pages.shape[-1] == hd and v_pages.shape[-1] == (hd if values_in_keys else vd)
+    assert not values_in_keys or (v_pages.data_ptr() == k_pages.data_ptr() and vd <= hd)
     assert sinks is None or (sinks.dtype == torch.float32 and sinks.shape == (nq,) and sinks.is_contiguous())
     lib = load_family("attention_simt")
-    _check(lib.wllm_paged_attention_simt_tiled_general(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages),
+    _check(lib.wllm_paged_attention_simt_tiled_strided(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages),
                                                        _ptr(v_pages), _dt(q), _ptr(_int32(req_q_start, "req_q_start")),
                                                        _ptr(_int32(req_q_len, "req_q_len")),
                                                        _ptr(_int32(req_ctx_len, "req_ctx_len")),
                                                        _ptr(_int32(block_table, "block_table")), block_table.shape[1],
                                                        req_q_len.shape[0], max_q_len, nq, nkv, hd, page_size, window,
-                                                       c_float(scale), vd, _ptr(sinks), c_float(cap), keep, _stream()),
+                                                       c_float(scale), vd, _ptr(sinks), c_float(cap), keep,
+                                                       hd if values_in_keys else 0, _stream()),
            f"paged_attention_simt_tiled(head_dim={hd}/{vd}, heads={nq}/{nkv})")
     return out
 
@@ -484,12 +566,50 @@ def gated_act(gate_up: torch.Tensor, out: torch.Tensor, act: str, limit: float =
     return out
 
 
-def tanh_cap(x: torch.Tensor, cap: float) -> torch.Tensor:
-    """x <- cap * tanh(x / cap), in place on a contiguous 32-bit tensor."""
+def tanh_cap(x: torch.Tensor, cap: float, scale: float = 1.0) -> torch.Tensor:
+    """x <- cap * tanh(x * scale / cap), in place on a contiguous 32-bit tensor."""
     _need_cuda(x)
     assert x.dtype == torch.float32 and x.is_contiguous() and cap > 0
     lib = load_family("activation")
-    _check(lib.wllm_tanh_cap(_ptr(x), ctypes.c_longlong(x.numel()), c_float(cap), _stream()), "tanh_cap")
+    _check(lib.wllm_scale_tanh_cap(_ptr(x), ctypes.c_longlong(x.numel()), c_float(cap), c_float(scale), _stream()), "tanh_cap")
+    return x
+
+
+def scale_rows(x: torch.Tensor, scale: float) -> torch.Tensor:
+    """x <- x * scale, in place on a contiguous 32-bit tensor."""
+    _need_cuda(x)
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    lib = load_family("activation")
+    _check(lib.wllm_scale_tanh_cap(_ptr(x), ctypes.c_longlong(x.numel()), c_float(0.0), c_float(scale), _stream()), "scale_rows")
+    return x
+
+
+UNIT_ACTIVATIONS = {"relu_squared": 0}
+
+
+def unit_act(x: torch.Tensor, out: torch.Tensor, act: str) -> torch.Tensor:
+    """out = act(x) elementwise for a feed-forward without a gate; 'relu_squared': max(x, 0)^2, 32-bit, rounded once."""
+    _need_cuda(x, out)
+    assert x.is_contiguous() and out.is_contiguous() and out.shape == x.shape and out.dtype == x.dtype
+    code = UNIT_ACTIVATIONS.get(act)
+    if code is None:
+        raise KernelError(f"activation {act!r} not supported ({', '.join(UNIT_ACTIVATIONS)})")
+    lib = load_family("activation")
+    _check(lib.wllm_unit_act(_ptr(x), _ptr(out), _dt(x), code, ctypes.c_longlong(x.numel()), _stream()), "unit_act")
+    return out
+
+
+def sigmoid_gate(x: torch.Tensor, fused: torch.Tensor, parts: int, col0: int) -> torch.Tensor:
+    """x[n, c] *= sigmoid(gate[n, c]) in place, the gate being columns col0 .. col0 + x.shape[1] of the fused projection
+    `fused` [n, W] (or float32 partial sums [parts, n, W], added in order)."""
+    _need_cuda(x, fused)
+    n, width = x.shape
+    ptr, dt, row_stride, nparts, part_stride, rows = _fused_args(fused, parts)
+    assert rows == n and x.stride(1) == 1 and col0 + width <= fused.shape[-1]
+    lib = load_family("activation")
+    item = 4 if fused.dtype == torch.float32 else 2
+    _check(lib.wllm_sigmoid_gate(_ptr(x), _dt(x), x.stride(0), c_void_p(fused.data_ptr() + col0 * item), dt, row_stride, nparts,
+                                 part_stride, n, width, _stream()), "sigmoid_gate")
     return x
 
 
@@ -534,7 +654,8 @@ def fma_peak_tflops(device, iters: int = 20000) -> float:
     return best
 
 
-_TC_EPILOGUES = {"bf16": 0, "f32": 1, "gelu_tanh": 2, "silu": 3, "relu": 4, "capped_swish": 5}
+_TC_EPILOGUES = {"bf16": 0, "f32": 1, "gelu_tanh": 2, "silu": 3, "relu": 4, "capped_swish": 5, "relu_squared": 6}
+_TC_GATED = (2, 3, 4, 5)
 _tc_status: dict = {}
 
 
@@ -625,7 +746,7 @@ def gemm_bf16_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = No
                  limit: float = 0.0, slope: float = 0.0) -> torch.Tensor:
     """out = a @ w^T on tcgen05 tensor cores (csrc/gemm_bf16_tc.cu).  epilogue 'bf16' | 'f32' (32-bit out) |
     'gelu_tanh' | 'silu' | 'relu' (w = [gate; up] stacked: out[M, N/2] = act(a gate^T) * (a up^T)) | 'capped_swish' (the
-    clamped gated unit of gated_act, with its `limit` and `slope`).
+    clamped gated unit of gated_act, with its `limit` and `slope`) | 'relu_squared' (no gate: out[M, N] = max(a w^T, 0)^2).
     k_splits > 1 ('f32' only) cuts K into parts; `out` is then [k_splits, M, N] partial sums.
     half_rows: the tile of products of at most 128 rows (see tile_plan, which chooses it when None)."""
     _need_cuda(a, w, out)
@@ -636,7 +757,7 @@ def gemm_bf16_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = No
     N = w.shape[0]
     assert w.shape[1] == K
     code = _TC_EPILOGUES[epilogue]
-    cols = N // 2 if code >= 2 else N
+    cols = N // 2 if code in _TC_GATED else N
     shape = (M, cols) if k_splits == 1 else (k_splits, M, cols)
     if out is None:
         out = torch.empty(shape, dtype=torch.float32 if code == 1 else torch.bfloat16, device=a.device)
@@ -647,7 +768,7 @@ def gemm_bf16_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = No
         max_ctas = sm_count()
     lib = load_family("gemm_bf16_tc")
     if half_rows is None:
-        half_rows = tile_plan(M, N, K, code >= 2, k_splits > 1)[0]
+        half_rows = tile_plan(M, N, K, code in _TC_GATED, k_splits > 1)[0]
     _check(lib.wllm_gemm_bf16_tc_params(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(-2), M, N, K, code,
                                         k_splits, half_rows, _ptr(status), max_ctas, c_float(limit), c_float(slope), _stream()),
            f"gemm_bf16_tc({M}x{N}x{K}, {epilogue}, {k_splits} parts)")
@@ -721,6 +842,18 @@ def gated_linear(a: torch.Tensor, w_gate_up: torch.Tensor, act: str, out: torch.
         return gemm_bf16_tc(a, w_gate_up, out, act, checked=True, limit=limit, slope=slope)
     gu = linear(a, w_gate_up, scratch((a.shape[0], w_gate_up.shape[0]), a.dtype))
     return gated_act(gu, out, act, limit, slope)
+
+
+def unit_linear(a: torch.Tensor, w_up: torch.Tensor, act: str, out: torch.Tensor, scratch) -> torch.Tensor:
+    """out[n, I] = act(a @ up^T) for a feed-forward without a gate ('relu_squared').  bfloat16: one tensor-memory GEMM
+    whose epilogue applies the activation on the 32-bit sums; otherwise product, then activation kernel
+    (`scratch(shape, dtype)` supplies the [n, I] intermediate)."""
+    if act not in UNIT_ACTIVATIONS:
+        raise KernelError(f"activation {act!r} not supported ({', '.join(UNIT_ACTIVATIONS)})")
+    if a.dtype == torch.bfloat16 and tc_gemm_ok(a, w_up):
+        return gemm_bf16_tc(a, w_up, out, act, checked=True)
+    h = linear(a, w_up, scratch((a.shape[0], w_up.shape[0]), a.dtype))
+    return unit_act(h, out, act)
 
 
 def _fused_args(fused, parts: int):

@@ -16,7 +16,13 @@ y / sqrt(mean(y^2) + eps), before the scores), softcap (c: a score becomes c * t
 keep_first (with a window: the first keys of a sequence stay visible behind it, at their true positions: key j
 is seen from position i when j <= i and (i - j < window or j < keep_first)), reads_other_cache (the mixer has no key
 and value projections, names no k_proj and v_proj, and must stand in a run that reads another run's cache; its queries,
-mask, scale and cap are its own).
+mask, scale and cap are its own), mask ('window', the default: `window` counts the latest keys; 'blocks': `window` is
+the size of a block, and position i sees key j <= i when both lie in the same block of that many positions, blocks
+counted from position 0 of the sequence), row_norm ({"q": name, "k": name, "eps": e}: the token's whole query row, all
+heads at once, is divided by its root mean square and multiplied by the gain of that name, the key row likewise, in
+front of the rotary turn), gate_proj (checkpoint name of a matrix [num_heads * value_dim, hidden]: the heads' outputs are
+multiplied by the sigmoid of that projection of the mixer's input before the output projection; the gate is computed by
+the same product as q, k and v).
 
 A mixer may be one of several that read the same input (a block that runs two mixers side
 by side): `input_weights()` lists the matrices that read the input, `mix(fused, parts,
@@ -54,6 +60,16 @@ class PagedAttention:
         self.keep_first = int(spec.options.get("keep_first") or 0) if self.window else 0
         if self.softcap < 0 or self.keep_first < 0:
             raise ValueError("softcap and keep_first must not be negative")
+        mask = spec.options.get("mask") or "window"
+        if mask not in ("window", "blocks"):
+            raise ValueError(f"mask {mask!r}: 'window' or 'blocks'")
+        self.blocks = mask == "blocks" and bool(self.window)
+        if self.blocks and (self.keep_first or self.borrows):
+            raise ValueError("a mask of blocks keeps no first keys and reads no other run's cache")
+        self.row_norm = spec.options.get("row_norm")
+        self.gate_name = spec.options.get("gate_proj")
+        if self.row_norm is not None and self.borrows:
+            raise ValueError("row norms of q and k need the mixer's own key projection")
         self.position = POSITIONS.build(spec.position)
         self.vd = int(spec.options.get("value_dim") or self.hd)
         scale = spec.options.get("scale")
@@ -67,15 +83,17 @@ class PagedAttention:
             raise ValueError(f"head size {self.hd_file}: heads that are divided by their root mean square come in steps of 8 elements")
         self.sink_name = spec.options.get("sink")
         self.unit_norm_eps = spec.options.get("qk_unit_norm_eps")
-        # the tensor-core kernels take keys and values of one size; other shapes run on the general kernels
-        self.general = self.vd != self.hd
-        # columns of the fused q|k|v row (q alone in a mixer that reads another's keys and values)
-        self.width = self.nq * self.hd if self.borrows else (self.nq + self.nkv) * self.hd + self.nkv * self.vd
+        # the tensor-core kernels take keys and values of one size and know windows, not blocks; other cases run on the general kernels
+        self.general = self.vd != self.hd or self.blocks
+        # columns of the fused q|k|v row (q alone in a mixer that reads another's keys and values), the gate's behind them
+        self.qkv_width = self.nq * self.hd if self.borrows else (self.nq + self.nkv) * self.hd + self.nkv * self.vd
+        self.width = self.qkv_width + (self.nq * self.vd if self.gate_name is not None else 0)
+        self.q_gain = self.k_gain = None
         self.tag = ""                    # set by a mixer that runs this one beside another: keeps their buffers apart
         self.wqkv = self.wo = self.sinks = None
 
     def cache_need(self):
-        return KVNeed(self.nkv, self.hd, self.window, self.vd if self.vd != self.hd else None, self.keep_first)
+        return KVNeed(self.nkv, self.hd, self.window, self.vd if self.vd != self.hd else None, self.keep_first, blocks=self.blocks)
 
     def param_specs(self):
         H, n = self.hidden_size, self.names
@@ -84,6 +102,11 @@ class PagedAttention:
             out[1:1] = [ParamSpec(n["k_proj"], (self.nkv * self.hd_file, H)), ParamSpec(n["v_proj"], (self.nkv * self.vd_file, H))]
         if self.sink_name is not None:
             out.append(ParamSpec(self.sink_name, (self.nq,), "vector"))
+        if self.gate_name is not None:
+            out.append(ParamSpec(self.gate_name, (self.nq * self.vd_file, H)))
+        if self.row_norm is not None:
+            out += [ParamSpec(self.row_norm["q"], (self.nq * self.hd_file,), "vector"),
+                    ParamSpec(self.row_norm["k"], (self.nkv * self.hd_file,), "vector")]
         return out
 
     def load(self, fetch):
@@ -100,6 +123,12 @@ class PagedAttention:
         else:
             self.wqkv = torch.cat([wq, heads_padded(fetch(n["k_proj"]), self.nkv, self.hd_file, self.hd),
                                    heads_padded(fetch(n["v_proj"]), self.nkv, self.vd_file, self.vd)], dim=0).contiguous()
+        if self.gate_name is not None:
+            self.wqkv = torch.cat([self.wqkv, heads_padded(fetch(self.gate_name), self.nq, self.vd_file, self.vd)], dim=0).contiguous()
+        if self.row_norm is not None:
+            gains = [heads_padded(fetch(self.row_norm[k])[:, None], heads, self.hd_file, self.hd)[:, 0].contiguous()
+                     for k, heads in (("q", self.nq), ("k", self.nkv))]
+            self.q_gain, self.k_gain = gains
         wo = fetch(n["o_proj"])
         self.wo = heads_padded(wo.t().contiguous(), self.nq, self.vd_file, self.vd).t().contiguous()
         if self.sink_name is not None:
@@ -127,17 +156,29 @@ class PagedAttention:
             extra["vd"] = self.vd
         if self.unit_norm_eps is not None:
             extra["unit_norm_eps"] = float(self.unit_norm_eps)
-        ops.rope_kv_write(qkv, q, ctx.positions, ctx.group_slots[cache.group] if cache.writes else None,
-                          self.position.inv_freq, k_pages, v_pages, self.nq, 0 if self.borrows else self.nkv, self.hd,
-                          self.position.rotary_dim, group.page_size, in_splits=parts,
-                          pairing=getattr(self.position, "pairing", "half"), **extra)
+        slots = ctx.group_slots[cache.group] if cache.writes else None
+        pairing = getattr(self.position, "pairing", "half")
+        if self.row_norm is not None:
+            if self.unit_norm_eps is not None:
+                raise ValueError("q and k are normed either as whole rows or head by head, not both")
+            ops.rope_row_norm_kv_write(qkv, q, ctx.positions, slots, self.position.inv_freq, k_pages, v_pages, self.nq, self.nkv,
+                                       self.hd, self.position.rotary_dim, group.page_size, self.q_gain, self.k_gain,
+                                       float(self.row_norm["eps"]), self.nq * self.hd_file, self.nkv * self.hd_file,
+                                       in_splits=parts, pairing=pairing, vd=self.vd)
+        else:
+            ops.rope_kv_write(qkv[..., :self.qkv_width] if self.width != self.qkv_width else qkv, q, ctx.positions, slots,
+                              self.position.inv_freq, k_pages, v_pages, self.nq, 0 if self.borrows else self.nkv, self.hd,
+                              self.position.rotary_dim, group.page_size, in_splits=parts, pairing=pairing, **extra)
         attn = ctx.buffer(self.tag + "attn", (n, self.nq * self.vd), self.model_dtype)
         self.attend(q, attn, k_pages, v_pages, ctx, cache.group)
+        if self.gate_name is not None:
+            ops.sigmoid_gate(attn, qkv, parts, self.qkv_width)
         return as_branch(ops.project(attn, self.wo, lambda name, shape, dt: ctx.buffer(self.tag + "branch_" + name, shape, dt)))
 
     def attend(self, q, out, k_pages, v_pages, ctx, group: int) -> None:
         """Attention of every token of the step over its request's pages of cache group `group`."""
-        nq, nkv, hd, window, scale = self.nq, self.nkv, self.hd, self.window or 0, self.scale
+        nq, nkv, hd, scale = self.nq, self.nkv, self.hd, self.scale
+        window = -self.window if self.blocks else (self.window or 0)     # the kernels take a block size as a negative window
         ps, table = ctx.cache.page_size, ctx.group_tables[group]
         if q.dtype != torch.bfloat16 or not ops.mma_head_dim_ok(hd) or self.general:
             # Three kernels with one result, bit for bit, so the choice is one of speed alone.  Portions of prompts:

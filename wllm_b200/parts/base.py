@@ -77,6 +77,9 @@ class KVNeed:
     window: int | None = None
     v_head_dim: int | None = None    # size of a value head when it differs from head_dim
     keep_first: int = 0              # with a window: the sequence's first keys that stay visible behind it
+    blocks: bool = False             # `window` is the size of a block: a token reads the earlier keys of its own block of
+                                     # that many positions (blocks counted from position 0) instead of the latest keys
+    values_in_keys: bool = False     # a token's value is the first v_head_dim elements of its key's row: one pool holds both
 
 
 @dataclass(frozen=True)

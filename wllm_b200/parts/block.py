@@ -13,6 +13,13 @@ The norm behind a sublayer acts on the branch alone; it is left pending on the r
 next norm of the residual runs it, the add and itself in one kernel (`norm.branch` does it alone where that cannot be).  `feed_forward` may be None: the block then has its first sublayer only.
 
 spec options: norm_in, mixer, norm_mixer_out, and norm_post, feed_forward, norm_ff_out (all three or none).
+
+'branch_normed': a norm behind each sublayer and none in front; the sublayers read the residual as it is,
+    x = x + norm_mixer_out(mixer(x));  x = x + norm_ff_out(feed_forward(x))
+`reader` is the part that hands the residual to a sublayer (kind 'identity': the pending branch's norm, the add and the
+rounding to the model's element type in one kernel).  `feed_forward` may be None.
+
+spec options: reader, mixer, norm_mixer_out, and feed_forward, norm_ff_out (both or none).
 """
 from __future__ import annotations
 
@@ -67,3 +74,30 @@ class SandwichBlock:
         residual.pending = NormedBranch(self.mixer(self.norm_in(residual, ctx), ctx, cache), self.norm_mixer_out)
         if self.feed_forward is not None:
             residual.pending = NormedBranch(self.feed_forward(self.norm_post(residual, ctx), ctx), self.norm_ff_out)
+
+
+@BLOCKS.register("branch_normed")
+class BranchNormedBlock:
+    graph_safe = True
+
+    def __init__(self, spec, hidden_size: int, model_dtype):
+        kw = dict(hidden_size=hidden_size, model_dtype=model_dtype)
+        self.reader = NORMS.build(spec.reader, **kw)
+        self.mixer = MIXERS.build(spec.mixer, **kw)
+        self.norm_mixer_out = NORMS.build(spec.norm_mixer_out, **kw)
+        self.feed_forward = None
+        if spec.options.get("feed_forward") is not None:
+            self.feed_forward = FEED_FORWARDS.build(spec.feed_forward, **kw)
+            self.norm_ff_out = NORMS.build(spec.norm_ff_out, **kw)
+
+    def parts(self):
+        first = [self.reader, self.mixer, self.norm_mixer_out]
+        return first if self.feed_forward is None else first + [self.feed_forward, self.norm_ff_out]
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def __call__(self, residual: Residual, ctx, cache: CacheRef) -> None:
+        residual.pending = NormedBranch(self.mixer(self.reader(residual, ctx), ctx, cache), self.norm_mixer_out)
+        if self.feed_forward is not None:
+            residual.pending = NormedBranch(self.feed_forward(self.reader(residual, ctx), ctx), self.norm_ff_out)

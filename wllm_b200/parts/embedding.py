@@ -6,8 +6,9 @@ element type (src/wllm/models/llama.py:397-403, src/wllm/models/gemma.py:158-162
 so under bfloat16 the factor is the bfloat16 value nearest to the square root; the
 product itself goes to the 32-bit residual unrounded.
 A further option, position_table (checkpoint name) with max_positions: a learned row per position, added unscaled.
-Head spec options: tied (bool), weight (checkpoint name when not tied), vocab_size, softcap (c: the logits become
-c * tanh(logits / c), in 32-bit; absent or None: as they are).
+Head spec options: tied (bool), weight (checkpoint name when not tied), vocab_size, scale (a factor on the logits, in
+32-bit; absent: 1), softcap (c: the logits become c * tanh(logits / c), in 32-bit, after the factor; absent or None: as
+they are).
 The tied head multiplies by the unscaled table (src/wllm/models/llama.py:443-446) and
 is evaluated only at the rows whose logits are wanted; logits are 32-bit.
 """
@@ -65,6 +66,8 @@ class LogitsHead:
         self.weight = None
         cap = spec.options.get("softcap")
         self.softcap = None if cap is None else float(cap)
+        scale = spec.options.get("scale")
+        self.scale = 1.0 if scale is None else float(scale)
 
     def param_specs(self):
         return [] if self.tied else [ParamSpec(self.weight_name, (self.vocab, self.hidden_size), "table")]
@@ -76,4 +79,6 @@ class LogitsHead:
         if self.weight is None:
             self.weight = self.embedding.table
         logits = ops.linear(hidden_rows, self.weight, f32_out=True)
-        return logits if self.softcap is None else ops.tanh_cap(logits, self.softcap)
+        if self.softcap is None:
+            return logits if self.scale == 1.0 else ops.scale_rows(logits, self.scale)
+        return ops.tanh_cap(logits, self.softcap, self.scale)

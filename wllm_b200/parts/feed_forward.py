@@ -1,4 +1,6 @@
-"""Gated dense feed-forward: down(act(gate(x)) * up(x)).
+"""Dense feed-forwards: gated, down(act(gate(x)) * up(x)), and plain, down(act(up(x))).
+
+Kind 'gated_dense'.
 
 spec options: intermediate_size, activation ('gelu_tanh' for Gemma's GeGLU,
 src/wllm/models/gemma.py:54-62; 'silu'; 'relu'; 'capped_swish' with `limit` and `slope`: the unit
@@ -6,6 +8,9 @@ g = min(gate x, limit), u = clamp(up x, -limit, limit), down(g * sigmoid(slope g
 gate_proj/up_proj/down_proj (checkpoint names).  gate and up are stored as one matrix [2 I, hidden] (gate rows first).  Under
 bfloat16 one tensor-memory GEMM computes both products and applies act(gate) * up in its
 epilogue, in 32-bit on the accumulators; otherwise one product feeds the activation kernel.
+
+Kind 'dense' (no gate).  spec options: intermediate_size, activation ('relu_squared': max(z, 0)^2), up_proj/down_proj
+(checkpoint names).  Under bfloat16 the activation is the epilogue of the up product, on the 32-bit accumulators.
 """
 from __future__ import annotations
 
@@ -45,4 +50,32 @@ class GatedDense:
         h = ops.gated_linear(x, self.wgu, self.activation, ctx.buffer("ffn_act", (n, self.inter), self.model_dtype),
                              lambda shape, dtype: ctx.buffer("gate_up", shape, dtype),
                              **({"limit": self.limit, "slope": self.slope} if self.activation == "capped_swish" else {}))
+        return as_branch(ops.project(h, self.wd, lambda name, shape, dt: ctx.buffer("branch_" + name, shape, dt)))
+
+
+@FEED_FORWARDS.register("dense")
+class Dense:
+    graph_safe = True
+
+    def __init__(self, spec, hidden_size: int, model_dtype: torch.dtype):
+        self.inter = int(spec.intermediate_size)
+        self.activation = spec.activation
+        if self.activation not in ops.UNIT_ACTIVATIONS:
+            raise ValueError(f"activation {self.activation!r}: one of {', '.join(ops.UNIT_ACTIVATIONS)}")
+        self.hidden_size, self.model_dtype = hidden_size, model_dtype
+        self.names = {k: spec.options[k] for k in ("up_proj", "down_proj")}
+        self.wu = self.wd = None
+
+    def param_specs(self):
+        H, I, n = self.hidden_size, self.inter, self.names
+        return [ParamSpec(n["up_proj"], (I, H)), ParamSpec(n["down_proj"], (H, I))]
+
+    def load(self, fetch):
+        self.wu = fetch(self.names["up_proj"]).contiguous()
+        self.wd = fetch(self.names["down_proj"]).contiguous()
+
+    def __call__(self, x: torch.Tensor, ctx):
+        n = x.shape[0]
+        h = ops.unit_linear(x, self.wu, self.activation, ctx.buffer("ffn_act", (n, self.inter), self.model_dtype),
+                            lambda shape, dtype: ctx.buffer("ffn_up", shape, dtype))
         return as_branch(ops.project(h, self.wd, lambda name, shape, dt: ctx.buffer("branch_" + name, shape, dt)))
