@@ -113,7 +113,7 @@ def attention(m, w, p, h, eps):
     v = (h @ w[p + "v"].T).view(n, G, dv)
     q, k = turn_neighbours(q, pos, m.get("rot")), turn_neighbours(k, pos, m.get("rot"))
     seen = seen_in_blocks(n, m["mask"]["size"]) if m.get("mask") else seen_all(n)
-    mixed = softmax_heads(q, k, v, m["scale"], seen)
+    mixed = softmax_heads(q, k, v, m.get("scale", d ** -0.5), seen)
     return (mixed * torch.sigmoid(h @ w[p + "g"].T)) @ w[p + "o"].T
 
 
@@ -130,7 +130,7 @@ def latent_attention(m, w, p, h, eps):
     seen = seen_in_window(n, m["mask"]["size"]) if m.get("mask") else seen_all(n)
     heads = []
     for a in range(H):
-        s = (q_plain[:, a] @ k_plain[:, a].T + q_turned[:, a] @ shared[:, 0].T) * m["scale"]
+        s = (q_plain[:, a] @ k_plain[:, a].T + q_turned[:, a] @ shared[:, 0].T) * m.get("scale", (d + r) ** -0.5)
         s = s.masked_fill(~seen, float("-inf"))
         heads.append(torch.softmax(s, dim=-1) @ v[:, a])
     return torch.cat(heads, dim=-1) @ w[p + "o"].T
@@ -149,7 +149,7 @@ def owner(cfg, i):
 def layers(cfg, w, tokens):
     """The residual stream after the embedding's layers, one entry per layer run: [runs, n, width]."""
     eps = cfg["norm"]["eps"]
-    x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)] * cfg["embedding"]["scale"]
+    x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)] * (cfg.get("embedding") or {}).get("scale", 1.0)
     out = []
     for i, layer in enumerate(cfg["layers"]):
         p = f"l{owner(cfg, i)}."
