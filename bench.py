@@ -748,6 +748,195 @@ def taritar_bench(args) -> int:
     return 0
 
 
+ZAFILIX_SIZES = {
+    # width, feed-forward, attention (heads, kv heads, head size) in blocks, latent attention (heads, plain, turning, value, latent row) in a window
+    "2k": dict(width=2048, ff=8192, attn=(16, 4, 128), block=1024, latent=(16, 128, 64, 128, 512), window=1024, vocab=32000),
+    "4k": dict(width=4096, ff=14336, attn=(32, 8, 128), block=1024, latent=(32, 128, 64, 128, 512), window=1024, vocab=32000),
+}
+
+
+def zafilix_config(size: dict) -> dict:
+    """Four layer runs: attention in blocks, latent attention in a window, and each once more on the same tensors."""
+    nq, nkv, hd = size["attn"]
+    H, dim, rot, vd, rank = size["latent"]
+    att = {"type": "attention", "mlp": {"kind": "dense", "ff": size["ff"]},
+           "mixer": {"heads": nq, "kv_heads": nkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": size["block"]},
+                     "rot": {"dims": hd, "base": 500000.0, "scaling": {"factor": 8.0}}}}
+    lat = {"type": "latent_attention", "mlp": {"kind": "dense", "ff": size["ff"]},
+           "mixer": {"heads": H, "dim": dim, "rot_dim": rot, "vdim": vd, "kv_rank": rank, "scale": (dim + rot) ** -0.5,
+                     "mask": {"size": size["window"]}, "rot": {"dims": rot, "base": 10000.0}}}
+    return {"architecture": "Zafilix", "vocab": size["vocab"], "width": size["width"], "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+            "logit_scale": 0.5, "logit_softcap": 30.0, "layers": [att, lat, dict(att, weights_of=0), dict(lat, weights_of=1)]}
+
+
+def zafilix_kernel_table(size: dict, pk: dict, T: int, batch: int, context: int) -> dict:
+    """Zafilix's kernels alone at one size's shapes beside the like kernels of the Gemma layer: microseconds, the time the
+    bytes each must move (or its arithmetic) take at the measured peaks (`floor_us`), and how many times that it takes."""
+    import torch
+    from wllm_b200.kernels import ops
+    dev, bf, f32, i32 = "cuda:0", torch.bfloat16, torch.float32, torch.int32
+    flush = torch.zeros(160 << 20, dtype=f32, device=dev)
+    W, ff = size["width"], size["ff"]
+    nq, nkv, hd = size["attn"]
+    H, dim, rot, vd, rank = size["latent"]
+    block, window = size["block"], size["window"]
+    row_len = rank + rot
+    ps = 64
+    out = {}
+
+    def row(name, fn, bytes_moved, flops=0.0):
+        us = timed_us(fn, flush)
+        floor = max(bytes_moved / (pk["hbm_gbs"] * 1e3), flops / (pk["bf16_tflops"] * 1e6))
+        out[name] = {"us": round(us, 1), "floor_us": round(floor, 2), "x_floor": round(us / max(floor, 1e-9), 1)}
+    g = torch.Generator(device=dev).manual_seed(1)
+
+    def rnd(*shape, dtype=f32, scale=1.0):
+        return (torch.randn(*shape, generator=g, device=dev, dtype=f32) * scale).to(dtype)
+
+    def held(store):
+        return lambda name, sh, dt: store.setdefault((name, sh), torch.empty(sh, dtype=dt, device=dev))
+    # ---- the norm: Gemma's in front of a sublayer; Zafilix's behind one, with the add and the rounded copy the next sublayer reads
+    for n, tag in ((T, "prefill"), (batch, "decode")):
+        resid, delta, w = rnd(n, W), rnd(n, W, dtype=bf), rnd(W, dtype=bf)
+        o = torch.empty(n, W, dtype=bf, device=dev)
+        row(f"{tag}/gemma rmsnorm+add", lambda: ops.rmsnorm(resid, delta, w, 1e-6, 1.0, o), n * W * (4 + 4 + 2 + 2))
+        row(f"{tag}/norm behind the sublayer+add+rounded copy", lambda: ops.sandwich_norm(resid, (delta, 0), o, w, False, 1e-6, None, 0.0, False, 0.0,
+                                                                                         post_offset=1.0), n * W * (4 + 4 + 2 + 2))
+    # ---- rotary + cache write: Gemma's; rows normed as wholes first; the latent row and the queries' parts
+    pages = batch * (-(-(context + 1) // ps)) + -(-T // ps) + 1
+    kp, vp = rnd(pages, nkv, ps, hd, dtype=bf), rnd(pages, nkv, ps, hd, dtype=bf)
+    lp = rnd(pages, 1, ps, row_len, dtype=bf)
+    inv_freq = torch.arange(hd // 2, device=dev, dtype=f32).neg().div(hd // 2).exp()
+    inv_rot = torch.arange(rot // 2, device=dev, dtype=f32).neg().div(rot // 2).exp()
+    q_gain, k_gain, l_gain = rnd(nq * hd, dtype=bf), rnd(nkv * hd, dtype=bf), rnd(rank, dtype=bf)
+    for n, tag in ((T, "prefill"), (batch, "decode")):
+        qkv = rnd(n, (nq + 2 * nkv) * hd, dtype=bf)
+        qo = torch.empty(n, nq * hd, dtype=bf, device=dev)
+        pos = torch.arange(n, dtype=i32, device=dev)
+        moved = n * (nq + 2 * nkv) * hd * 2 * 2
+        row(f"{tag}/gemma rotary+cache write", lambda: ops.rope_kv_write(qkv, qo, pos, pos, inv_freq, kp, vp, nq, nkv, hd, hd, ps), moved)
+        row(f"{tag}/row norms+rotary of neighbours+cache write",
+            lambda: ops.rope_row_norm_kv_write(qkv, qo, pos, pos, inv_freq, kp, vp, nq, nkv, hd, hd, ps, q_gain, k_gain, 1e-6, nq * hd, nkv * hd,
+                                               pairing="interleaved"), moved)
+        fused = rnd(n, H * (dim + rot) + row_len, dtype=bf)
+        q_plain, q_mapped = torch.empty(n, H * dim, dtype=bf, device=dev), torch.empty(n, H * row_len, dtype=bf, device=dev)
+        row(f"{tag}/latent row (norm, turn, cache write) and the queries' parts",
+            lambda: ops.latent_prepare(fused, 0, pos, pos, inv_rot, l_gain, 1e-6, lp, ps, q_plain, q_mapped, H, dim, rot, rot, rank, row_len),
+            n * (H * (dim + rot) + row_len) * 2 * 2)
+        w_uk, w_uv = rnd(H, rank, dim, dtype=bf, scale=0.05), rnd(H, vd, rank, dtype=bf, scale=0.05)
+        mixed, heads_out = rnd(n, H, rank, dtype=bf), torch.empty(n, H, vd, dtype=bf, device=dev)
+        row(f"{tag}/latent: the keys' map on the queries", lambda: ops.head_linear(q_plain.view(n, H, dim), w_uk, q_mapped.view(n, H, row_len)[:, :, :rank]),
+            H * rank * dim * 2 + n * H * (dim + rank) * 2, 2.0 * n * H * dim * rank)
+        row(f"{tag}/latent: the values' map on the outputs", lambda: ops.head_linear(mixed, w_uv, heads_out),
+            H * rank * vd * 2 + n * H * (vd + rank) * 2, 2.0 * n * H * vd * rank)
+        gate_in = rnd(n, nq * hd * 2, dtype=bf)
+        attn = rnd(n, nq * hd, dtype=bf)
+        row(f"{tag}/sigmoid gate on the heads' outputs", lambda: ops.sigmoid_gate(attn, gate_in, 0, nq * hd), n * nq * hd * 2 * 3)
+    # ---- attention over a prompt of T tokens: Gemma's over all keys and in a window; in blocks; over latent rows in a window
+    one = torch.ones(1, dtype=i32, device=dev)
+    table = torch.arange(-(-T // ps), dtype=i32, device=dev).view(1, -1)
+    q, ao = rnd(T, nq * hd, dtype=bf), torch.empty(T, nq * hd, dtype=bf, device=dev)
+    in_window = sum(min(p + 1, window) for p in range(T))
+    in_block = sum(p % block + 1 for p in range(T))
+    row("prefill/gemma attention (all keys)", lambda: ops.attention_mma_prefill(q, ao, kp, vp, one * 0, one * T, one * T, table, T, nq, nkv, hd, ps, 0,
+                                                                                 hd ** -0.5, skip_single=False), T * nq * hd * 4, 4.0 * nq * hd * T * T / 2)
+    row("prefill/gemma attention (window)", lambda: ops.attention_mma_prefill(q, ao, kp, vp, one * 0, one * T, one * T, table, T, nq, nkv, hd, ps, window,
+                                                                               hd ** -0.5, skip_single=False), T * nq * hd * 4, 4.0 * nq * hd * in_window)
+    row("prefill/attention in blocks", lambda: ops.attention_mma_prefill(q, ao, kp, vp, one * 0, one * T, one * T, table, T, nq, nkv, hd, ps, -block,
+                                                                          hd ** -0.5, skip_single=False), T * nq * hd * 4, 4.0 * nq * hd * in_block)
+    ql, mixed_l = rnd(T, H * row_len, dtype=bf, scale=0.2), torch.empty(T, H * rank, dtype=bf, device=dev)
+    pos_t, req_t = torch.arange(T, dtype=i32, device=dev), torch.zeros(T, dtype=i32, device=dev)
+    latent_flops = 2.0 * H * (row_len + rank) * in_window
+    if hasattr(ops, "latent_mma_ok") and ops.latent_mma_ok(H, rank, row_len, ps):
+        row("prefill/attention over latent rows (window, tensor cores)",
+            lambda: ops.latent_attention_mma(ql, mixed_l, lp, one * 0, one * T, one * T, table, T, H, rank, row_len, ps, window, (dim + rot) ** -0.5),
+            T * H * (row_len + rank) * 2, latent_flops)
+    if T * H <= 8192:       # the general kernel, a warp a row: minutes of its time would say nothing new
+        row("prefill/attention over latent rows (window, general kernel)",
+            lambda: ops.paged_attention_simt(ql, mixed_l, lp, lp, req_t, pos_t, table, H, 1, row_len, ps, window, (dim + rot) ** -0.5, vd=rank,
+                                             values_in_keys=True), T * H * (row_len + rank) * 2, latent_flops)
+    # ---- one decoded token of `batch` requests over `context` cached tokens
+    per = -(-(context + 1) // ps)
+    dtable = torch.arange(batch * per, dtype=i32, device=dev).view(batch, per)
+    qd, od = rnd(batch, nq * hd, dtype=bf), torch.empty(batch, nq * hd, dtype=bf, device=dev)
+    starts, lens = torch.arange(batch, dtype=i32, device=dev), torch.ones(batch, dtype=i32, device=dev)
+    ctxs = lens * context
+    split_keys, max_splits = ops.decode_split_plan(batch * nkv, -(-context // 512) * 512, 32 if hd % 64 == 0 else 64)
+    scratch = torch.empty(ops.attention_mma_scratch_floats(batch, nq, hd, max_splits), device=dev)
+    read_w, read_b = min(context, window), (context - 1) % block + 1
+    for what, win, read in (("gemma attention (all keys)", 0, context), ("gemma attention (window)", window, read_w), ("attention in blocks", -block, read_b)):
+        row(f"decode/{what}", lambda: ops.attention_mma_decode(qd, od, kp, vp, starts, lens, ctxs, dtable, nq, nkv, hd, ps, win, hd ** -0.5,
+                                                               split_keys, max_splits, scratch), batch * read * nkv * hd * 2 * 2)
+    qdl, odl = rnd(batch, H * row_len, dtype=bf, scale=0.2), torch.empty(batch, H * rank, dtype=bf, device=dev)
+    dpos = (ctxs - 1).to(i32)
+    chunks = ops.simt_chunks(context, window)
+    lscratch = torch.empty(batch * H * chunks * (rank + 2), device=dev)
+    latent_bytes = batch * read_w * row_len * 2 + batch * H * (row_len + rank) * 2
+    row("decode/attention over latent rows (window, general kernel, keys in chunks)",
+        lambda: ops.paged_attention_simt(qdl, odl, lp, lp, starts, dpos, dtable, H, 1, row_len, ps, window, (dim + rot) ** -0.5, lscratch, chunks,
+                                         vd=rank, values_in_keys=True), latent_bytes, 2.0 * batch * H * (row_len + rank) * read_w)
+    if hasattr(ops, "latent_mma_ok") and ops.latent_mma_ok(H, rank, row_len, ps):
+        row("decode/attention over latent rows (window, tensor cores)",
+            lambda: ops.latent_attention_mma(qdl, odl, lp, starts, lens, ctxs, dtable, 1, H, rank, row_len, ps, window, (dim + rot) ** -0.5),
+            latent_bytes, 2.0 * batch * H * (row_len + rank) * read_w)
+    # ---- feed-forward: Gemma's gated unit; up with the squared ReLU; down
+    for n, tag in ((T, "prefill"), (batch, "decode")):
+        x = rnd(n, W, dtype=bf)
+        wgu, wu, wd = rnd(2 * ff, W, dtype=bf, scale=0.02), rnd(ff, W, dtype=bf, scale=0.02), rnd(W, ff, dtype=bf, scale=0.02)
+        act, gu = torch.empty(n, ff, dtype=bf, device=dev), torch.empty(n, 2 * ff, dtype=bf, device=dev)
+        row(f"{tag}/gemma gate|up with tanh-GELU", lambda: ops.gated_linear(x, wgu, "gelu_tanh", act, lambda sh, dt: gu),
+            2 * ff * W * 2 + n * (W + ff) * 2, 4.0 * n * ff * W)
+        row(f"{tag}/up with the squared ReLU", lambda: ops.unit_linear(x, wu, "relu_squared", act, lambda sh, dt: gu[:, :ff]),
+            ff * W * 2 + n * (W + ff) * 2, 2.0 * n * ff * W)
+        parts = {}
+        row(f"{tag}/down", lambda: ops.project(act, wd, held(parts)), ff * W * 2 + n * (W + ff) * 2, 2.0 * n * ff * W)
+    return out
+
+
+def zafilix_bench(args) -> int:
+    import torch
+    from wllm_b200.config import EngineConfig, GemmaConfig, ZafilixConfig
+    from wllm_b200.engine import build_model
+    pk = peaks()
+    ps, T = args.page_size, 2048
+    context = args.context or 2048
+    engine_cfg = EngineConfig(dtype="bfloat16", block_size=ps, max_num_seqs=max(64, args.batch), cuda_graphs=not args.no_graphs)
+    sizes = {}
+    for name in (args.sizes if args.sizes != "2b,7b" else "2k,4k").split(","):
+        size = ZAFILIX_SIZES[name]
+        nq, nkv, hd = size["attn"]
+        raw = zafilix_config(size)
+        models = {
+            "gemma": GemmaConfig.from_dict(dict(architectures=["GemmaForCausalLM"], vocab_size=size["vocab"], hidden_size=size["width"],
+                                                intermediate_size=size["ff"], num_hidden_layers=len(raw["layers"]),
+                                                num_attention_heads=nq, num_key_value_heads=nkv, head_dim=hd,
+                                                max_position_embeddings=16384)),
+            "zafilix": ZafilixConfig.from_dict(raw),
+        }
+        res = {}
+        for label, cfg in models.items():
+            model = build_model(None, engine_cfg.dtype, engine_cfg.device, config=cfg, random_seed=1)
+            pre_ms = prefill_run(model, engine_cfg, T, ps)
+            ms, launches, _, clocks, _ = decode_run(model, engine_cfg, args.batch, context, min(args.steps, 32), args.warmup, ps, 3)
+            res[label] = {"weights_gb": round(model.weight_bytes() / 1e9, 3), "prefill_tok_s": round(T / (pre_ms / 1e3), 1),
+                          "prefill_ms": round(pre_ms, 3), "decode_tok_s": round(args.batch / (ms / 1e3), 1),
+                          "decode_ms_per_step": round(ms, 4), "decode_launches": launches,
+                          "decode_weights_hbm_frac": round(model.weight_bytes() / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 3), "clocks": clocks}
+            del model
+            torch.cuda.empty_cache()
+        sizes[name] = {"shape": size, "models": res}
+        if not args.no_points:
+            sizes[name]["kernels"] = zafilix_kernel_table(size, pk, T, args.batch, context)
+    print(json.dumps({"metric": "Zafilix beside Gemma at equal layer sizes: prefill tok/s @ 2048 tokens, decode tok/s",
+                      "design": "zafilix", "unit": "tokens/s", "n_gpus": 1, "steps": min(args.steps, 32), "warmup": args.warmup,
+                      "dtype": "bf16", "data": "synthetic (random weights, random token ids, random cached keys/values)",
+                      "config": {"global_batch": args.batch, "seq_len": context, "prefill_tokens": T, "page_size": ps,
+                                 "cuda_graphs": not args.no_graphs, "peaks": pk["source"],
+                                 "l2": "kernel table: a 640 MB buffer is written before every timed launch"},
+                      "peaks": pk, "sizes": sizes}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -762,9 +951,9 @@ def main() -> int:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--regions", type=int, default=5, help="timed regions of --steps steps each; the median is reported")
-    ap.add_argument("--design", default="gemma", choices=["gemma", "pesanex", "taritar"],
-                    help="gemma: the default workload; pesanex, taritar: models of that design beside a Gemma of equal layer sizes (another line)")
-    ap.add_argument("--sizes", default="2b,7b", help="--design pesanex: which of the layer sizes to run (2b, 7b)")
+    ap.add_argument("--design", default="gemma", choices=["gemma", "pesanex", "taritar", "zafilix"],
+                    help="gemma: the default workload; pesanex, taritar, zafilix: models of that design beside a Gemma of equal layer sizes (another line)")
+    ap.add_argument("--sizes", default="2b,7b", help="which of the layer sizes to run (--design pesanex: 2b, 7b; taritar, zafilix: 2k, 4k)")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
@@ -776,6 +965,8 @@ def main() -> int:
         return pesanex_bench(args)
     if args.design == "taritar":
         return taritar_bench(args)
+    if args.design == "zafilix":
+        return zafilix_bench(args)
     import torch
     from wllm_b200.config import EngineConfig, GemmaConfig
     from wllm_b200.engine import build_model

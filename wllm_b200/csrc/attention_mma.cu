@@ -402,7 +402,7 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
     const int split = blockIdx.z, g = blockIdx.y, r = blockIdx.x;     // CTAs start request by request, the last (shortest) splits last
     if (req_q_len[r] != 1) return;
     const int ctx = req_ctx_len[r], pos = ctx - 1;
-    int first = window > 0 ? max(0, pos - window + 1) : 0;
+    int first = first_visible_key(pos, window);
     int kept = 0;               // the sequence's first keys that stay visible behind the window (none, or the two runs touch)
     if (keep > 0) { if (first <= keep) first = 0; else kept = keep; }
     const int part_keys = keys_per_split(ctx, split_keys, max_splits, SPLIT_TILE);
@@ -533,7 +533,7 @@ decode_ws_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ ou
     const int split = blockIdx.z, g = blockIdx.y, r = blockIdx.x;     // CTAs start request by request, the last (shortest) splits last
     if (req_q_len[r] != 1) return;
     const int ctx = req_ctx_len[r], pos = ctx - 1;
-    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+    const int first = first_visible_key(pos, window);
     const int part_keys = keys_per_split(ctx, split_keys, max_splits, SPLIT_TILE);
     const int num_splits = (ctx + part_keys - 1) / part_keys;
     if (split >= num_splits) return;
@@ -787,7 +787,7 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
     const int last_row = min(rows, row0 + BM) - 1;
     const int pos_hi = pos0 + last_row / rep;
     const int pos_lo = pos0 + row0 / rep;
-    int key_lo = window > 0 ? max(0, pos_lo - window + 1) : 0, kept_cta = 0;
+    int key_lo = first_visible_key(pos_lo, window), kept_cta = 0;
     const int key_hi = pos_hi + 1;
     // a sequence's first `keep` keys stay visible behind the window; where they touch the window there is one run from 0
     if (keep > 0) { if (key_lo <= keep) key_lo = 0; else kept_cta = keep; }
@@ -797,7 +797,7 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
     for (int i = 0; i < 2; ++i) {
         const int m = row0 + warp * 16 + (lane >> 2) + i * 8;
         pos_r[i] = m < rows ? pos0 + m / rep : -1;                      // a row past the end sees no key
-        first_r[i] = window > 0 ? max(0, pos_r[i] - window + 1) : 0;
+        first_r[i] = first_visible_key(pos_r[i], window);
         kept_r[i] = 0;
         if (keep > 0) { if (first_r[i] <= keep) first_r[i] = 0; else kept_r[i] = keep; }
     }

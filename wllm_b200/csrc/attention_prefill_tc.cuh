@@ -78,7 +78,7 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
 
     const int last_row = min(rows, row0 + TC_BM) - 1;
     const int pos_hi = pos0 + last_row / rep, pos_lo = pos0 + row0 / rep;
-    int key_lo = window > 0 ? max(0, pos_lo - window + 1) : 0, kept_cta = 0;
+    int key_lo = first_visible_key(pos_lo, window), kept_cta = 0;
     const int key_hi = pos_hi + 1;
     // `keep` > 0: a sequence's first keys stay visible behind the window.  Where they touch the window the keys are one run from
     // 0; else the tiles of the kept keys that lie before the window's first tile are walked first: place n of the walk is
@@ -212,7 +212,7 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
         }
 
         const int pos_row = m_row < rows ? pos0 + m_row / rep : -1;            // a row past the end sees no key
-        int first_row = window > 0 ? max(0, pos_row - window + 1) : 0, kept_row = 0;
+        int first_row = first_visible_key(pos_row, window), kept_row = 0;
         if (keep > 0) { if (first_row <= keep) first_row = 0; else kept_row = keep; }
         const float sc = capl > 0.f ? 1.0f : scale2;          // capped scores are in log2 units already
         const float cap_in = capl > 0.f ? 2.0f * scale2 / capl : 0.f;
@@ -461,7 +461,7 @@ prefill_pair_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
     // the keys that the pair's 256 rows see
     const int last_row = min(rows, (tile + 1) * 2 * TC_BM) - 1;
     const int pos_hi = pos0 + last_row / rep, pos_lo = pos0 + (tile * 2 * TC_BM) / rep;
-    int key_lo = window > 0 ? max(0, pos_lo - window + 1) : 0, kept_cta = 0;
+    int key_lo = first_visible_key(pos_lo, window), kept_cta = 0;
     const int key_hi = pos_hi + 1;
     // `keep` > 0: a sequence's first keys stay visible behind the window.  Where they touch the window the keys are one run from
     // 0; else the tiles of the kept keys that lie before the window's first tile are walked first: place n of the walk is
@@ -598,7 +598,7 @@ prefill_pair_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
         if (lane == 0) mbar_arrive_cluster(lead_q_full);
 
         const int pos_row = m_row < rows ? pos0 + m_row / rep : -1;            // a row past the end sees no key
-        int first_row = window > 0 ? max(0, pos_row - window + 1) : 0, kept_row = 0;
+        int first_row = first_visible_key(pos_row, window), kept_row = 0;
         if (keep > 0) { if (first_row <= keep) first_row = 0; else kept_row = keep; }
         const float sc = capl > 0.f ? 1.0f : scale2;          // capped scores are in log2 units already
         const float cap_in = capl > 0.f ? 2.0f * scale2 / capl : 0.f;

@@ -328,8 +328,8 @@ WLLM_API int wllm_paged_attention_simt_strided(const void* q, int q_stride, void
     if (v_ld == 0) v_ld = vd;
     if (v_ld < vd) return WLLM_BAD_SIZE;
     if (keep < 0 || cap < 0.f || (keep > 0 && window <= 0)) return WLLM_BAD_SIZE;
-    // key rows are read with 16-byte loads: head sizes come in steps of 8 up to 512
-    if (hd <= 0 || hd > 512 || hd % 8 != 0 || vd <= 0 || vd > 512 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 ||
+    // key rows are read with 16-byte loads: key heads come in steps of 8 up to 1024, value heads up to 512
+    if (hd <= 0 || hd > 1024 || hd % 8 != 0 || vd <= 0 || vd > 512 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 ||
         max_pages <= 0)
         return WLLM_BAD_SIZE;
     if (scratch != nullptr && (max_chunks < 1 || max_chunks > 65535)) return WLLM_BAD_SIZE;

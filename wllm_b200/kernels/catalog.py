@@ -23,6 +23,8 @@ FAMILIES = {
     # tensor-core attention is built per head size; others are built when a model first asks
     "attention_mma": [{"HEAD_DIM": 256}, {"HEAD_DIM": 32}, {"HEAD_DIM": 48}],
     "attention_decode_static": [{"HEAD_DIM": 256}],
+    # attention over latent rows on the tensor cores is built per row and value size, when a model first asks
+    "latent_attention_mma": [],
 }
 
 

@@ -315,15 +315,25 @@ def latent_prepare(fused: torch.Tensor, parts: int, positions: torch.Tensor, slo
            "latent_prepare")
 
 
+HEAD_LINEAR_BATCHED_ROWS = 32     # bfloat16 steps of this many tokens or more: the heads' maps are one batched matrix product
+
+
 def head_linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
     """y[t, h, :] = x[t, h, :] @ w[h]^T for every head h.  x [n, heads, K] and y [n, heads, N] may be views (free row and
-    head strides, unit inner stride); w [heads, N, K] contiguous.  32-bit accumulation, every output one ascending chain
-    over K (csrc/latent_attention.cu)."""
+    head strides, unit inner stride); w [heads, N, K] contiguous.  32-bit accumulation.  float32, and bfloat16 steps of
+    few tokens: every output is one ascending chain over K (csrc/latent_attention.cu); bfloat16 steps of more tokens:
+    a batched product of the vendor's matrix library, as `linear` uses it."""
     _need_cuda(x, w, y)
     n, heads, K = x.shape
     N = w.shape[1]
     assert w.shape == (heads, N, K) and w.is_contiguous() and y.shape == (n, heads, N)
     assert x.stride(2) == 1 and y.stride(2) == 1 and x.dtype == w.dtype == y.dtype
+    if x.dtype == torch.bfloat16 and n >= HEAD_LINEAR_BATCHED_ROWS:
+        # one strided batched product of the vendor's matrix library, 32-bit accumulation, written in place: [heads, n, K] x [heads, K, N]
+        global launches
+        launches += 1
+        torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out=y.transpose(0, 1))
+        return y
     lib = load_family("latent_attention")
     _check(lib.wllm_head_linear(_ptr(x), x.stride(0), x.stride(1), _ptr(w), _ptr(y), y.stride(0), y.stride(1), _dt(x), n, heads,
                                 N, K, _stream()), f"head_linear({n}x{heads}x{N}x{K})")
@@ -331,6 +341,33 @@ def head_linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> torch.Tens
 
 
 SIMT_CHUNK = 64    # keys per chunk of the one-warp-per-row attention (csrc/attention_simt.cu)
+
+
+def latent_mma_ok(heads: int, rank: int, row: int, page_size: int) -> bool:
+    """Sizes that the tensor-core attention over latent rows is built for (one build per row and value size)."""
+    return heads > 0 and rank % 32 == 0 and 32 <= rank <= 512 and row % 8 == 0 and rank <= row <= 832 and \
+        page_size > 0 and page_size & (page_size - 1) == 0
+
+
+def latent_attention_mma(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, req_q_start: torch.Tensor,
+                         req_q_len: torch.Tensor, req_ctx_len: torch.Tensor, block_table: torch.Tensor, max_q_len: int,
+                         heads: int, rank: int, row: int, page_size: int, window: int, scale: float,
+                         skip_single: bool = False) -> torch.Tensor:
+    """bfloat16 attention of every request's new tokens over its cached latent rows (csrc/latent_attention_mma.cu).
+    q: [n, heads * row]; pages: [pool pages, 1, page_size, row], a row's first `rank` elements being its value;
+    out: [n, heads * rank].  `window` as for `paged_attention_simt`."""
+    _need_cuda(q, out, pages, req_q_start, req_q_len, req_ctx_len, block_table)
+    assert q.dtype == torch.bfloat16 == out.dtype == pages.dtype and q.stride(1) == 1 and out.stride(1) == 1
+    assert pages.is_contiguous() and pages.shape[-1] == row and pages.shape[-2] == page_size and block_table.dim() == 2
+    assert q.shape[1] == heads * row and out.shape[1] == heads * rank and latent_mma_ok(heads, rank, row, page_size)
+    lib = load_family("latent_attention_mma", {"LATENT_ROW": row, "LATENT_RANK": rank})
+    _check(lib.wllm_latent_attention_mma(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(pages),
+                                         _ptr(_int32(req_q_start, "req_q_start")), _ptr(_int32(req_q_len, "req_q_len")),
+                                         _ptr(_int32(req_ctx_len, "req_ctx_len")), _ptr(_int32(block_table, "block_table")),
+                                         block_table.shape[1], req_q_len.shape[0], max_q_len, heads, page_size, window,
+                                         c_float(scale), 1 if skip_single else 0, _stream()),
+           f"latent_attention_mma(row={row}, rank={rank}, heads={heads})")
+    return out
 
 
 def simt_chunks(max_ctx: int, window: int, keep: int = 0) -> int:

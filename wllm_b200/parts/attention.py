@@ -83,8 +83,8 @@ class PagedAttention:
             raise ValueError(f"head size {self.hd_file}: heads that are divided by their root mean square come in steps of 8 elements")
         self.sink_name = spec.options.get("sink")
         self.unit_norm_eps = spec.options.get("qk_unit_norm_eps")
-        # the tensor-core kernels take keys and values of one size and know windows, not blocks; other cases run on the general kernels
-        self.general = self.vd != self.hd or self.blocks
+        # the tensor-core kernels take keys and values of one size; other cases run on the general kernels
+        self.general = self.vd != self.hd
         # columns of the fused q|k|v row (q alone in a mixer that reads another's keys and values), the gate's behind them
         self.qkv_width = self.nq * self.hd if self.borrows else (self.nq + self.nkv) * self.hd + self.nkv * self.vd
         self.width = self.qkv_width + (self.nq * self.vd if self.gate_name is not None else 0)
@@ -213,7 +213,9 @@ class PagedAttention:
             ops.attention_mma_decode(q, out, k_pages, v_pages, ctx.req_q_start, ctx.req_q_len, ctx.req_ctx_len, table,
                                      nq, nkv, hd, ps, window, scale, split_keys, max_splits, scratch, **extra)
         if ctx.num_multi > 0 or not decode:
-            split_above, halves = (0, None) if listed else self._shared_tiles(ctx, skip_single=decode)
+            # two CTAs share a tile only where both halves hold keys of every row: not with a list of tiles, and not with
+            # blocks, where the rows behind a block's border see no key of the tile's first half
+            split_above, halves = (0, None) if listed or self.blocks else self._shared_tiles(ctx, skip_single=decode)
             ops.attention_mma_prefill(q, out, k_pages, v_pages, ctx.req_q_start, ctx.req_q_len, ctx.req_ctx_len, table,
                                       ctx.max_q_len, nq, nkv, hd, ps, window, scale, skip_single=decode,
                                       split_above=split_above, halves=halves, **extra)

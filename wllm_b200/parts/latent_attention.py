@@ -95,10 +95,16 @@ class LatentAttention:
 
     def attend(self, q, out, pages, ctx, group: int) -> None:
         """Every token of the step over its request's cached rows: one key/value head for all query heads, the values
-        inside the keys' rows.  The three kernels of the general family give one result, bit for bit (portions of
-        prompts: 32 rows share every tile of keys; few rows over long contexts: a warp per row and chunk of keys)."""
+        inside the keys' rows.  bfloat16 steps that bring portions of prompts run on the tensor cores (64 rows of a
+        request share every tile of keys).  The three kernels of the general family give one result, bit for bit
+        (portions of prompts: 32 rows share every tile of keys; few rows over long contexts: a warp per row and chunk
+        of keys)."""
         H, row, R, window = self.heads, self.row, self.rank, self.window or 0
         ps, table = ctx.cache.page_size, ctx.group_tables[group]
+        if ctx.num_multi > 0 and self.model_dtype == torch.bfloat16 and ops.latent_mma_ok(H, R, row, ps):
+            ops.latent_attention_mma(q, out, pages, ctx.req_q_start, ctx.req_q_len, ctx.req_ctx_len, table, ctx.max_q_len,
+                                     H, R, row, ps, window, self.scale)
+            return
         if ctx.num_multi > 0 and row <= 256 and R % 8 == 0:
             ops.paged_attention_simt_tiled(q, out, pages, pages, ctx.req_q_start, ctx.req_q_len, ctx.req_ctx_len, table,
                                            ctx.max_q_len, H, 1, row, ps, window, self.scale, vd=R, values_in_keys=True)
