@@ -847,7 +847,7 @@ def zafilix_kernel_table(size: dict, pk: dict, T: int, batch: int, context: int)
     ql, mixed_l = rnd(T, H * row_len, dtype=bf, scale=0.2), torch.empty(T, H * rank, dtype=bf, device=dev)
     pos_t, req_t = torch.arange(T, dtype=i32, device=dev), torch.zeros(T, dtype=i32, device=dev)
     latent_flops = 2.0 * H * (row_len + rank) * in_window
-    if hasattr(ops, "latent_mma_ok") and ops.latent_mma_ok(H, rank, row_len, ps):
+    if ops.latent_mma_ok(H, rank, row_len, ps):
         row("prefill/attention over latent rows (window, tensor cores)",
             lambda: ops.latent_attention_mma(ql, mixed_l, lp, one * 0, one * T, one * T, table, T, H, rank, row_len, ps, window, (dim + rot) ** -0.5),
             T * H * (row_len + rank) * 2, latent_flops)
@@ -875,9 +875,12 @@ def zafilix_kernel_table(size: dict, pk: dict, T: int, batch: int, context: int)
     row("decode/attention over latent rows (window, general kernel, keys in chunks)",
         lambda: ops.paged_attention_simt(qdl, odl, lp, lp, starts, dpos, dtable, H, 1, row_len, ps, window, (dim + rot) ** -0.5, lscratch, chunks,
                                          vd=rank, values_in_keys=True), latent_bytes, 2.0 * batch * H * (row_len + rank) * read_w)
-    if hasattr(ops, "latent_mma_ok") and ops.latent_mma_ok(H, rank, row_len, ps):
-        row("decode/attention over latent rows (window, tensor cores)",
-            lambda: ops.latent_attention_mma(qdl, odl, lp, starts, lens, ctxs, dtable, 1, H, rank, row_len, ps, window, (dim + rot) ** -0.5),
+    if ops.latent_mma_ok(H, rank, row_len, ps):
+        split_tiles, lat_splits = ops.latent_split_plan(batch, H, -(-context // ps) * ps, window)
+        mscratch = torch.empty(ops.latent_mma_scratch_floats(batch, H, rank, lat_splits), device=dev)
+        row("decode/attention over latent rows (window, tensor cores, keys in splits)",
+            lambda: ops.latent_attention_mma(qdl, odl, lp, starts, lens, ctxs, dtable, 1, H, rank, row_len, ps, window, (dim + rot) ** -0.5,
+                                             split_tiles=split_tiles, max_splits=lat_splits, scratch=mscratch),
             latent_bytes, 2.0 * batch * H * (row_len + rank) * read_w)
     # ---- feed-forward: Gemma's gated unit; up with the squared ReLU; down
     for n, tag in ((T, "prefill"), (batch, "decode")):

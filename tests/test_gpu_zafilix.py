@@ -424,10 +424,12 @@ def test_rows_normed_as_wholes_then_turned_in_neighbouring_pairs(nq, nkv, hd, vd
         ops.rope_row_norm_kv_write(x.to(DEV), q_out, positions.to(DEV), slots.to(DEV), table, kp, vp, nq, nkv, hd, rot, ps, q_gain.to(DEV),
                                    k_gain.to(DEV), eps, nq * hd, nkv * hd, in_splits=parts, pairing="interleaved", vd=vd)
         tol = 2e-5 if dtype == torch.float32 else 0.04
-        assert (q_out.cpu().double().view(n, nq, hd) - q).abs().max() < tol * float(q.abs().max())
+        # the angle is a 32-bit product: at position 4095 it is rounded to a few 1e-4 of a radian, which the 64-bit statement is not
+        turned = max(tol, 3e-4)
+        assert (q_out.cpu().double().view(n, nq, hd) - q).abs().max() < turned * float(q.abs().max())
         for t in range(n):
             page, at = int(slots[t]) // ps, int(slots[t]) % ps
-            assert (kp[page, :, at].cpu().double() - k[t]).abs().max() < tol * float(k.abs().max())
+            assert (kp[page, :, at].cpu().double() - k[t]).abs().max() < (turned if positions[t] > 100 else tol) * float(k.abs().max())
             assert (vp[page, :, at].cpu().double() - v[t]).abs().max() < tol * float(v.abs().max())
         for page, at in ((0, 2), (0, 3), (2, 0), (2, 2), (2, 3), (3, 2), (3, 3)):                # no other slot was written
             assert float(kp[page, :, at].abs().max()) == 0 and float(vp[page, :, at].abs().max()) == 0
@@ -618,3 +620,15 @@ def test_tensor_core_attention_over_latent_rows(window, rank, rot, H):
             for what, a, b in (("portion", got[:n], want), ("whole", got[n:n + 70], want_short), ("single", got[n + 70:], want_long)):
                 err = (a - b).abs().max()
                 assert err < 0.04, (what, ps, edge, float(err))
+            # single tokens alone: the last three positions of the sequence as three requests, their keys whole and in splits
+            R = 3
+            tables3 = table[:1].expand(R, -1).contiguous()
+            for split_tiles in (0, 1, 2, 5):
+                tiles = -(-L // 32) if window == 0 else min(-(-L // 32), -(-abs(window) // 32) + 1)
+                max_splits = -(-tiles // split_tiles) if split_tiles else 1
+                scratch = torch.full((ops.latent_mma_scratch_floats(R, H, rank, max_splits),), float("nan"), device=DEV) if split_tiles else None
+                od = torch.empty(R, H * rank, dtype=dtype, device=DEV)
+                ops.latent_attention_mma(qd[n - 3:n].contiguous(), od, pool, i32([0, 1, 2]), i32([1, 1, 1]), i32([L - 2, L - 1, L]), tables3, 1,
+                                         H, rank, row, ps, window, scale, split_tiles=split_tiles, max_splits=max_splits, scratch=scratch)
+                err = (od.cpu().double() - want[-3:]).abs().max()
+                assert err < 0.04, ("singles", ps, edge, split_tiles, float(err))

@@ -11,6 +11,7 @@
 //   wllm_latent_prepare   one CTA a token: the cache row (norm in 32-bit from the projection's partial sums, the turn in
 //                         32-bit), the queries' plain parts rounded for the product with Uk, their turned parts placed
 //                         behind the columns that product will fill
+//   wllm_head_linear_few  the same for bfloat16 steps of few tokens: a warp an output, the matrices read once.
 //   wllm_head_linear      y[n, h, :N] = x[n, h, :K] W_h^T for every head h: the two maps above.  Every output is one
 //                         ascending chain of fused multiply-adds over K in 32-bit, so a token's result does not depend on
 //                         the step it is computed in.
@@ -168,6 +169,63 @@ head_linear_kernel(const T* __restrict__ x, int x_row, int x_head, const T* __re
             if (j < N) y[(size_t)t * y_row + (size_t)h * y_head + j] = from_f32<T>(acc[a][b]);
         }
     }
+}
+
+// The same map for bfloat16 steps of few tokens (decoded tokens), where the matrices are what is read: a warp an output
+// (head h, column j) for up to HF_T tokens at once.  The lanes stride over K with 16-byte loads of w, each token's sum is
+// reduced over the lanes in a fixed order, so a token's result does not depend on the other tokens of the step.
+constexpr int HF_T = 8;
+
+__global__ void __launch_bounds__(256)
+head_linear_few_kernel(const bf16* __restrict__ x, int x_row, int x_head, const bf16* __restrict__ w, bf16* __restrict__ y,
+                       int y_row, int y_head, int n, int heads, int N, int K) {
+    pdl_begin();
+    const int lane = threadIdx.x & 31;
+    const long long out = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (out >= (long long)heads * N) return;
+    const int h = (int)(out / N), j = (int)(out % N);
+    const int t0 = blockIdx.y * HF_T, nt = min(HF_T, n - t0);
+    const bf16* wr = w + ((size_t)h * N + j) * K;
+    const bf16* xh = x + (size_t)t0 * x_row + (size_t)h * x_head;
+    float acc[HF_T];
+#pragma unroll
+    for (int t = 0; t < HF_T; ++t) acc[t] = 0.f;
+    for (int k = lane * 8; k < K; k += 256) {
+        const uint4 wv = *reinterpret_cast<const uint4*>(wr + k);
+        const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+        for (int t = 0; t < HF_T; ++t) {
+            if (t >= nt) continue;
+            const uint4 xv = *reinterpret_cast<const uint4*>(xh + (size_t)t * x_row + k);
+            const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 a = __bfloat1622float2(x2[e]), b = __bfloat1622float2(w2[e]);
+                acc[t] = fmaf(a.x, b.x, acc[t]);
+                acc[t] = fmaf(a.y, b.y, acc[t]);
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < HF_T; ++t) {
+        float v = acc[t];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0 && t < nt) y[(size_t)(t0 + t) * y_row + (size_t)h * y_head + j] = __float2bfloat16_rn(v);
+    }
+}
+
+// bfloat16, K and the strides of x in steps of 8 elements, 16-byte aligned x and w: steps of up to `few` tokens run a warp an output.
+WLLM_API int wllm_head_linear_few(const void* x, int x_row, int x_head, const void* w, void* y, int y_row, int y_head, int n,
+                                  int heads, int N, int K, cudaStream_t stream) {
+    if (n <= 0) return WLLM_OK;
+    if (heads <= 0 || N <= 0 || K <= 0 || K % 8 != 0 || x_row % 8 != 0 || x_head % 8 != 0) return WLLM_BAD_SIZE;
+    if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return WLLM_BAD_ALIGN;
+    const long long ctas = ((long long)heads * N + 7) / 8;
+    const int token_blocks = (n + HF_T - 1) / HF_T;
+    if (ctas > 0x7fffffffLL || token_blocks > 65535) return WLLM_BAD_SIZE;
+    return wllm_launch(head_linear_few_kernel, dim3((unsigned)ctas, token_blocks), 256, 0, stream, (const bf16*)x, x_row, x_head,
+                       (const bf16*)w, (bf16*)y, y_row, y_head, n, heads, N, K);
 }
 
 // x: element (t, h, k) at t * x_row + h * x_head + k; w [heads, N, K] contiguous; y: element (t, h, j) at t * y_row + h * y_head + j.

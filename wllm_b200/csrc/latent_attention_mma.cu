@@ -76,7 +76,8 @@ __global__ void __launch_bounds__(THREADS, 1)
 latent_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
                   const bf16* __restrict__ pages, const int* __restrict__ req_q_start, const int* __restrict__ req_q_len,
                   const int* __restrict__ req_ctx_len, const int* __restrict__ block_table, int max_pages, int heads,
-                  int page_size, int window, float scale2, int skip_single) {
+                  int page_size, int window, float scale2, int skip_single, int q_rows, int split_tiles, int max_splits,
+                  float* __restrict__ part_o, float* __restrict__ part_ml) {
     extern __shared__ unsigned char smem_raw[];
     pdl_begin();
     const int r = blockIdx.y;
@@ -84,7 +85,7 @@ latent_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
     if (q_len <= 0 || (skip_single && q_len == 1)) return;
     const int rows = q_len * heads;
     const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;        // the tiles with the most keys start first
-    const int row0 = tile * BM;
+    const int row0 = tile * q_rows;                                // q_rows: 64, or 16 in a launch whose requests have no more
     if (row0 >= rows) return;
     const int ctx = req_ctx_len[r], q_start = req_q_start[r], pos0 = ctx - q_len;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -95,10 +96,20 @@ latent_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
     const int page_shift = 31 - __clz(page_size);
 
     // the keys that the CTA's rows see: from the first row's first key to the last row's position
-    const int last_row = min(rows, row0 + BM) - 1;
+    const int last_row = min(rows, row0 + q_rows) - 1;
     const int pos_lo = pos0 + row0 / heads, pos_hi = pos0 + last_row / heads;
     const int key_lo = first_visible_key(pos_lo, window), key_hi = pos_hi + 1;
-    const int t0 = key_lo / BN, t1 = (key_hi + BN - 1) / BN;
+    int t0 = key_lo / BN, t1 = (key_hi + BN - 1) / BN;
+    // a single token's keys may be cut into splits of `split_tiles` tiles, one CTA each (blockIdx.z); the others run whole
+    int num_splits = 1;
+    if (split_tiles > 0 && q_len == 1) {
+        num_splits = (t1 - t0 + split_tiles - 1) / split_tiles;
+        if ((int)blockIdx.z >= num_splits) return;
+        t0 += (int)blockIdx.z * split_tiles;
+        t1 = min(t1, t0 + split_tiles);
+    } else if (blockIdx.z > 0) {
+        return;
+    }
 
     int pos_r[2], first_r[2];
 #pragma unroll
@@ -109,13 +120,13 @@ latent_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
     }
     // the keys that the warp's 16 rows see
     const int warp_first_row = row0 + group * 16;
-    const bool warp_has_rows = warp_first_row < rows;
+    const bool warp_has_rows = warp_first_row < rows && group * 16 < q_rows;
     const int warp_pos_lo = pos0 + min(rows - 1, warp_first_row) / heads;
     const int warp_pos_hi = pos0 + min(rows - 1, warp_first_row + 15) / heads;
     const int warp_key_lo = first_visible_key(warp_pos_lo, window);
 
     // the queries: row m is (token m / heads, head m % heads)
-    for (int idx = threadIdx.x; idx < BM * CPR_PAD; idx += THREADS) {
+    for (int idx = threadIdx.x; idx < q_rows * CPR_PAD; idx += THREADS) {
         const int row = idx / CPR_PAD, chunk = idx % CPR_PAD;
         const int m = row0 + row;
         const bool valid = m < rows && chunk < CPR;
@@ -220,15 +231,61 @@ latent_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
     }
+    if (num_splits > 1) {                 // this split's maximum, sum and unnormalised output; merged in split order afterwards
+        if (!warp_has_rows) return;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int m = group * 16 + (lane >> 2) + i * 8;             // row0 is 0: a single token's rows are its heads
+            if (m >= rows) continue;
+            const size_t at = ((size_t)r * max_splits + blockIdx.z) * heads + m;
+            if (half == 0 && (lane & 3) == 0) { part_ml[at * 2] = m_run[i]; part_ml[at * 2 + 1] = l_run[i]; }
+            float* dst = part_o + at * RANK + half * (RANK / 2) + (lane & 3) * 2;
+#pragma unroll
+            for (int n = 0; n < NTO; ++n) *reinterpret_cast<float2*>(dst + n * 8) = make_float2(o[n][2 * i], o[n][2 * i + 1]);
+        }
+        return;
+    }
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const int m = row0 + group * 16 + (lane >> 2) + i * 8;
-        if (m >= rows) continue;
+        if (m >= rows || !warp_has_rows) continue;
         const float inv = 1.0f / l_run[i];
         bf16* dst = out + (size_t)(q_start + m / heads) * out_stride + (size_t)(m % heads) * RANK + half * (RANK / 2) + (lane & 3) * 2;
 #pragma unroll
         for (int n = 0; n < NTO; ++n)
             *reinterpret_cast<__nv_bfloat162*>(dst + n * 8) = __floats2bfloat162_rn(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
+    }
+}
+
+// The splits of a single token's keys into one output row per head, in split order.
+__global__ void __launch_bounds__(128)
+latent_merge_kernel(bf16* __restrict__ out, int out_stride, const int* __restrict__ req_q_start, const int* __restrict__ req_q_len,
+                    const int* __restrict__ req_ctx_len, int heads, int window, int split_tiles, int max_splits,
+                    const float* __restrict__ part_o, const float* __restrict__ part_ml) {
+    pdl_begin();
+    const int h = blockIdx.x, r = blockIdx.y;
+    if (req_q_len[r] != 1) return;
+    const int pos = req_ctx_len[r] - 1;
+    const int t0 = first_visible_key(pos, window) / BN, t1 = (pos + BN) / BN;
+    const int num_splits = (t1 - t0 + split_tiles - 1) / split_tiles;
+    if (num_splits <= 1) return;
+    const size_t at0 = (size_t)r * max_splits * heads + h;
+    float top = -INFINITY;
+    for (int z = 0; z < num_splits; ++z) top = fmaxf(top, part_ml[(at0 + (size_t)z * heads) * 2]);
+    float sum = 0.f;
+    for (int z = 0; z < num_splits; ++z) {
+        const size_t at = at0 + (size_t)z * heads;
+        sum += part_ml[at * 2 + 1] * exp2f(part_ml[at * 2] - top);
+    }
+    const float inv = 1.0f / sum;
+    bf16* dst = out + (size_t)req_q_start[r] * out_stride + (size_t)h * RANK;
+    for (int c = threadIdx.x; c < RANK; c += 128) {
+        float acc = 0.f;
+        for (int z = 0; z < num_splits; ++z) {
+            const size_t at = at0 + (size_t)z * heads;
+            acc += part_o[at * RANK + c] * exp2f(part_ml[at * 2] - top);
+        }
+        dst[c] = __float2bfloat16_rn(acc * inv);
     }
 }
 
@@ -240,8 +297,11 @@ WLLM_API int wllm_latent_attention_mma_rank() { return RANK; }
 WLLM_API int wllm_latent_attention_mma(const void* q, int q_stride, void* out, int out_stride, const void* pages,
                                        const int* req_q_start, const int* req_q_len, const int* req_ctx_len,
                                        const int* block_table, int max_pages, int requests, int max_q_len, int heads,
-                                       int page_size, int window, float scale, int skip_single, cudaStream_t stream) {
+                                       int page_size, int window, float scale, int skip_single, int split_tiles, int max_splits,
+                                       float* scratch, cudaStream_t stream) {
     if (requests <= 0 || max_q_len <= 0) return WLLM_OK;
+    if (split_tiles < 0 || (split_tiles > 0 && (max_splits < 1 || max_splits > 65535 || scratch == nullptr || heads > BM)))
+        return WLLM_BAD_SIZE;
     if (heads <= 0 || page_size <= 0 || (page_size & (page_size - 1)) || max_pages <= 0 || requests > 65535) return WLLM_BAD_SIZE;
     if (q_stride % 8 != 0 || out_stride % 2 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)out & 3) || ((uintptr_t)pages & 15))
         return WLLM_BAD_ALIGN;
@@ -251,9 +311,24 @@ WLLM_API int wllm_latent_attention_mma(const void* q, int q_stride, void* out, i
         if (e != cudaSuccess) return 1000 + (int)e;
         configured = true;
     }
-    const long long tiles = ((long long)max_q_len * heads + BM - 1) / BM;
+    // a launch whose requests have at most 16 rows each keeps 16 query rows in shared memory: two CTAs fit an SM
+    const int q_rows = (long long)max_q_len * heads <= 16 ? 16 : BM;
+    const long long tiles = ((long long)max_q_len * heads + q_rows - 1) / q_rows;
     if (tiles > 0x7fffffffLL) return WLLM_BAD_SIZE;
-    return wllm_launch(latent_mma_kernel, dim3((unsigned)tiles, requests), THREADS, SMEM, stream, (const bf16*)q, q_stride,
-                       (bf16*)out, out_stride, (const bf16*)pages, req_q_start, req_q_len, req_ctx_len, block_table, max_pages,
-                       heads, page_size, window, scale * LOG2E, skip_single);
+    if (split_tiles == 0) max_splits = 1;
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + (size_t)requests * max_splits * heads * RANK : nullptr;
+    const int smem = 128 + q_rows * ROWB + STAGES * TILE_BYTES;
+    const int st = wllm_launch(latent_mma_kernel, dim3((unsigned)tiles, requests, max_splits), THREADS, smem, stream, (const bf16*)q,
+                               q_stride, (bf16*)out, out_stride, (const bf16*)pages, req_q_start, req_q_len, req_ctx_len, block_table,
+                               max_pages, heads, page_size, window, scale * LOG2E, skip_single, q_rows, split_tiles, max_splits,
+                               part_o, part_ml);
+    if (st || max_splits == 1) return st;
+    return wllm_launch(latent_merge_kernel, dim3(heads, requests), 128, 0, stream, (bf16*)out, out_stride, req_q_start, req_q_len,
+                       req_ctx_len, heads, window, split_tiles, max_splits, (const float*)part_o, (const float*)part_ml);
+}
+
+// Floats of scratch for `requests` single tokens whose keys are cut into up to `max_splits` splits.
+WLLM_API long long wllm_latent_attention_mma_scratch_floats(int requests, int heads, int max_splits) {
+    return (long long)requests * max_splits * heads * (RANK + 2);
 }

@@ -320,9 +320,9 @@ HEAD_LINEAR_BATCHED_ROWS = 32     # bfloat16 steps of this many tokens or more: 
 
 def head_linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
     """y[t, h, :] = x[t, h, :] @ w[h]^T for every head h.  x [n, heads, K] and y [n, heads, N] may be views (free row and
-    head strides, unit inner stride); w [heads, N, K] contiguous.  32-bit accumulation.  float32, and bfloat16 steps of
-    few tokens: every output is one ascending chain over K (csrc/latent_attention.cu); bfloat16 steps of more tokens:
-    a batched product of the vendor's matrix library, as `linear` uses it."""
+    head strides, unit inner stride); w [heads, N, K] contiguous.  32-bit accumulation.  float32: every output is one
+    ascending chain over K (csrc/latent_attention.cu); bfloat16 steps of few tokens: a warp an output, the matrices read
+    once; bfloat16 steps of more tokens: a batched product of the vendor's matrix library, as `linear` uses it."""
     _need_cuda(x, w, y)
     n, heads, K = x.shape
     N = w.shape[1]
@@ -335,6 +335,10 @@ def head_linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> torch.Tens
         torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out=y.transpose(0, 1))
         return y
     lib = load_family("latent_attention")
+    if x.dtype == torch.bfloat16 and K % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) % 8 == 0 and x.data_ptr() % 16 == 0:
+        _check(lib.wllm_head_linear_few(_ptr(x), x.stride(0), x.stride(1), _ptr(w), _ptr(y), y.stride(0), y.stride(1), n, heads, N, K,
+                                        _stream()), f"head_linear_few({n}x{heads}x{N}x{K})")
+        return y
     _check(lib.wllm_head_linear(_ptr(x), x.stride(0), x.stride(1), _ptr(w), _ptr(y), y.stride(0), y.stride(1), _dt(x), n, heads,
                                 N, K, _stream()), f"head_linear({n}x{heads}x{N}x{K})")
     return y
@@ -349,24 +353,54 @@ def latent_mma_ok(heads: int, rank: int, row: int, page_size: int) -> bool:
         page_size > 0 and page_size & (page_size - 1) == 0
 
 
+LATENT_TILE = 32    # keys per tile of the tensor-core attention over latent rows (csrc/latent_attention_mma.cu)
+
+
+@functools.lru_cache(maxsize=4096)
+def latent_split_plan(requests: int, heads: int, max_ctx: int, window: int) -> tuple:
+    """(split_tiles, max_splits) for a step of single tokens: every token's tiles of keys are cut into splits of
+    split_tiles tiles, a CTA each, so that the step fills the SMs about once (two CTAs fit an SM); (0, 1): no cut."""
+    most = -(-max(1, max_ctx) // LATENT_TILE)
+    tiles = most if window == 0 else min(most, -(-abs(window) // LATENT_TILE) + 1)
+    if heads > 64 or tiles <= 1:
+        return 0, 1
+    split_tiles = max(1, -(-tiles * requests // (2 * sm_count())), -(-tiles // 64))
+    max_splits = -(-tiles // split_tiles)
+    return (split_tiles, max_splits) if max_splits > 1 else (0, 1)
+
+
+def latent_mma_scratch_floats(requests: int, heads: int, rank: int, max_splits: int) -> int:
+    return requests * max_splits * heads * (rank + 2)
+
+
 def latent_attention_mma(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, req_q_start: torch.Tensor,
                          req_q_len: torch.Tensor, req_ctx_len: torch.Tensor, block_table: torch.Tensor, max_q_len: int,
                          heads: int, rank: int, row: int, page_size: int, window: int, scale: float,
-                         skip_single: bool = False) -> torch.Tensor:
+                         skip_single: bool = False, split_tiles: int = 0, max_splits: int = 1,
+                         scratch: torch.Tensor | None = None) -> torch.Tensor:
     """bfloat16 attention of every request's new tokens over its cached latent rows (csrc/latent_attention_mma.cu).
     q: [n, heads * row]; pages: [pool pages, 1, page_size, row], a row's first `rank` elements being its value;
-    out: [n, heads * rank].  `window` as for `paged_attention_simt`."""
-    _need_cuda(q, out, pages, req_q_start, req_q_len, req_ctx_len, block_table)
+    out: [n, heads * rank].  `window` as for `paged_attention_simt`.  split_tiles > 0 (see latent_split_plan; `scratch`
+    float32 of latent_mma_scratch_floats): the keys of requests that bring one token are cut into splits that a second
+    kernel merges in order."""
+    _need_cuda(q, out, pages, req_q_start, req_q_len, req_ctx_len, block_table, scratch)
     assert q.dtype == torch.bfloat16 == out.dtype == pages.dtype and q.stride(1) == 1 and out.stride(1) == 1
     assert pages.is_contiguous() and pages.shape[-1] == row and pages.shape[-2] == page_size and block_table.dim() == 2
     assert q.shape[1] == heads * row and out.shape[1] == heads * rank and latent_mma_ok(heads, rank, row, page_size)
+    if split_tiles > 0:
+        assert scratch is not None and scratch.dtype == torch.float32 and scratch.is_contiguous()
+        assert scratch.numel() >= latent_mma_scratch_floats(req_q_len.shape[0], heads, rank, max_splits)
     lib = load_family("latent_attention_mma", {"LATENT_ROW": row, "LATENT_RANK": rank})
     _check(lib.wllm_latent_attention_mma(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(pages),
                                          _ptr(_int32(req_q_start, "req_q_start")), _ptr(_int32(req_q_len, "req_q_len")),
                                          _ptr(_int32(req_ctx_len, "req_ctx_len")), _ptr(_int32(block_table, "block_table")),
                                          block_table.shape[1], req_q_len.shape[0], max_q_len, heads, page_size, window,
-                                         c_float(scale), 1 if skip_single else 0, _stream()),
+                                         c_float(scale), 1 if skip_single else 0, split_tiles, max_splits,
+                                         _ptr(scratch) if split_tiles > 0 else None, _stream()),
            f"latent_attention_mma(row={row}, rank={rank}, heads={heads})")
+    if split_tiles > 0 and max_splits > 1:
+        global launches
+        launches += 1    # the merge kernel
     return out
 
 

@@ -95,15 +95,23 @@ class LatentAttention:
 
     def attend(self, q, out, pages, ctx, group: int) -> None:
         """Every token of the step over its request's cached rows: one key/value head for all query heads, the values
-        inside the keys' rows.  bfloat16 steps that bring portions of prompts run on the tensor cores (64 rows of a
-        request share every tile of keys).  The three kernels of the general family give one result, bit for bit
+        inside the keys' rows.  bfloat16 steps run on the tensor cores (64 rows of a request share every tile of keys; a
+        step of single tokens cuts their keys into splits).  The three kernels of the general family give one result, bit for bit
         (portions of prompts: 32 rows share every tile of keys; few rows over long contexts: a warp per row and chunk
         of keys)."""
         H, row, R, window = self.heads, self.row, self.rank, self.window or 0
         ps, table = ctx.cache.page_size, ctx.group_tables[group]
-        if ctx.num_multi > 0 and self.model_dtype == torch.bfloat16 and ops.latent_mma_ok(H, R, row, ps):
+        if self.model_dtype == torch.bfloat16 and ops.latent_mma_ok(H, R, row, ps) and (ctx.num_multi > 0 or H <= 64):
+            split_tiles, max_splits, scratch = 0, 1, None
+            if ctx.num_multi == 0:          # single tokens alone: their keys in splits, so that few requests fill the SMs
+                requests = ctx.req_q_len.shape[0]
+                split_tiles, max_splits = ops.latent_split_plan(requests, H, ctx.max_ctx, window)
+                if split_tiles > 0:
+                    scratch = ctx.buffer(self.tag + "latent_splits", (ops.latent_mma_scratch_floats(requests, H, R, max_splits),),
+                                         torch.float32)
             ops.latent_attention_mma(q, out, pages, ctx.req_q_start, ctx.req_q_len, ctx.req_ctx_len, table, ctx.max_q_len,
-                                     H, R, row, ps, window, self.scale)
+                                     H, R, row, ps, window, self.scale, split_tiles=split_tiles, max_splits=max_splits,
+                                     scratch=scratch)
             return
         if ctx.num_multi > 0 and row <= 256 and R % 8 == 0:
             ops.paged_attention_simt_tiled(q, out, pages, pages, ctx.req_q_start, ctx.req_q_len, ctx.req_ctx_len, table,
