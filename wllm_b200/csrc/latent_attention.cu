@@ -81,10 +81,11 @@ latent_prepare_kernel(const TI* __restrict__ fused, int row_stride, int in_split
         for (int e = threadIdx.x; e < hd - rank; e += blockDim.x)
             dst[rank + e] = e < rot ? from_f32<TO>(turned([&](int i) { return in(qw + rank + i); }, e)) : from_f32<TO>(0.f);
     }
-    for (int item = threadIdx.x; item < heads * dim; item += blockDim.x) {
-        const int h = item / dim, c = item % dim;
-        q_plain[(size_t)t * heads * dim + item] = from_f32<TO>(in(h * (dim + rot) + c));
-    }
+    if (q_plain != nullptr)                   // null: the next product reads the plain parts from the fused row itself
+        for (int item = threadIdx.x; item < heads * dim; item += blockDim.x) {
+            const int h = item / dim, c = item % dim;
+            q_plain[(size_t)t * heads * dim + item] = from_f32<TO>(in(h * (dim + rot) + c));
+        }
     const int tail = hd - rank;
     for (int item = threadIdx.x; item < heads * tail; item += blockDim.x) {
         const int h = item / tail, e = item % tail;
@@ -95,7 +96,7 @@ latent_prepare_kernel(const TI* __restrict__ fused, int row_stride, int in_split
 }
 
 // fused [n, >= heads * (dim + rot) + rank + rot] (or `in_splits` 32-bit slabs), pages [page][1][slot][hd] with hd >= rank + rot,
-// q_plain [n, heads * dim], q_mapped [n, heads * hd] (columns rank .. hd of every head are written here), gain [rank].
+// q_plain [n, heads * dim] (or null), q_mapped [n, heads * hd] (columns rank .. hd of every head are written here), gain [rank].
 WLLM_API int wllm_latent_prepare(const void* fused, int in_dtype, int row_stride, int in_splits, long long in_split_stride,
                                  const int* positions, const int* slots, const float* inv_freq, const void* gain, int gain_dtype,
                                  float eps, void* pages, int page_size, void* q_plain, void* q_mapped, int out_dtype, int n,

@@ -417,6 +417,86 @@ rope_row_norm_kernel(const TI* __restrict__ qkv, int row_stride, int in_splits, 
     }
 }
 
+// The same for bfloat16 rows and gains whose heads, turned part and pitches come in steps of 8 elements: 16-byte loads and
+// stores, eight neighbouring elements a thread.  An element's partner is read from the row in shared memory, and the two
+// products of a turn are rounded apart as in rotate_pair, so an element gets the bits that the kernel above gives it
+// from the same sums of squares (the sums themselves are added up in another order here; a model always runs one of the two).
+__global__ void __launch_bounds__(256)
+rope_row_norm_vec_kernel(const bf16* __restrict__ qkv, int row_stride, bf16* __restrict__ q_out, int q_stride,
+                         const int* __restrict__ positions, const int* __restrict__ slots, const float* __restrict__ inv_freq,
+                         bf16* __restrict__ k_pages, bf16* __restrict__ v_pages, int nq, int nkv, int hd, int rot_dim,
+                         int page_size, int interleaved, int vd, const bf16* __restrict__ wq, const bf16* __restrict__ wk,
+                         int q_count, int k_count, float eps) {
+    extern __shared__ float row[];            // [(nq + nkv) * hd] the token's q and k parts, [half] sines, [half] cosines
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int slot = slots ? slots[t] : -1;
+    const float pos = (float)positions[t];
+    const int half = rot_dim >> 1, qw = nq * hd, kw = nkv * hd;
+    float* sn = row + qw + kw;
+    float* cs = sn + half;
+    for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf(pos * inv_freq[j], &sn[j], &cs[j]);
+    pdl_wait();
+    const bf16* x = qkv + (size_t)t * row_stride;
+    float ssq = 0.f, ssk = 0.f;
+    for (int c0 = threadIdx.x * 8; c0 < qw + kw; c0 += blockDim.x * 8) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(x + c0);
+        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 v = __bfloat1622float2(p2[e]);
+            row[c0 + 2 * e] = v.x; row[c0 + 2 * e + 1] = v.y;
+            ss += v.x * v.x; ss += v.y * v.y;
+        }
+        if (c0 < qw) ssq += ss; else ssk += ss;          // qw is a multiple of 8: a chunk lies on one side
+    }
+    ssq = block_sum(ssq, scratch);
+    ssk = block_sum(ssk, scratch);
+    const float inv_q = 1.0f / sqrtf(ssq / (float)q_count + eps);
+    const float inv_k = kw > 0 ? 1.0f / sqrtf(ssk / (float)k_count + eps) : 0.f;
+    const int heads = slot < 0 ? nq : nq + nkv, per_head = hd >> 3;
+    for (int item = threadIdx.x; item < heads * per_head; item += blockDim.x) {
+        const int h = item / per_head, c0 = (item % per_head) * 8;
+        const bool is_q = h < nq;
+        const float inv = is_q ? inv_q : inv_k;
+        const bf16* gain = is_q ? wq + h * hd : wk + (h - nq) * hd;
+        const float* src = row + h * hd;
+        const uint4 graw = *reinterpret_cast<const uint4*>(gain + c0);
+        const bf16* g8 = reinterpret_cast<const bf16*>(&graw);
+        float y[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int c = c0 + e;
+            const float mine = (src[c] * inv) * __bfloat162float(g8[e]);
+            y[e] = mine;
+            if (c < rot_dim) {
+                const bool first = interleaved ? !(c & 1) : c < half;
+                const int j = interleaved ? c >> 1 : (first ? c : c - half);
+                const int pc = interleaved ? c ^ 1 : (first ? c + half : c - half);
+                const float other = (src[pc] * inv) * __bfloat162float(gain[pc]);
+                const float a = __fmul_rn(mine, cs[j]), b = __fmul_rn(other, sn[j]);
+                y[e] = first ? __fsub_rn(a, b) : __fadd_rn(a, b);
+            }
+        }
+        uint4 packed;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(y[2 * e], y[2 * e + 1]);
+        bf16* dst = is_q ? q_out + (size_t)t * q_stride + (size_t)h * hd
+                         : k_pages + (((size_t)(slot / page_size) * nkv + (h - nq)) * page_size + slot % page_size) * hd;
+        *reinterpret_cast<uint4*>(dst + c0) = packed;
+    }
+    if (slot < 0) return;
+    const int v_per = vd >> 3;
+    for (int item = threadIdx.x; item < nkv * v_per; item += blockDim.x) {
+        const int kvh = item / v_per, c0 = (item % v_per) * 8;
+        *reinterpret_cast<uint4*>(v_pages + (((size_t)(slot / page_size) * nkv + kvh) * page_size + slot % page_size) * vd + c0) =
+            *reinterpret_cast<const uint4*>(x + qw + kw + kvh * vd + c0);
+    }
+}
+
 // wq [nq * hd], wk [nkv * hd]: the gains of the two row norms (one element type); q_count, k_count: the elements that
 // count for the means (nq * hd and nkv * hd unless the heads are held with zeros behind them).
 WLLM_API int wllm_rope_row_norm_kv_write(const void* qkv, int in_dtype, int row_stride, int in_splits, long long in_split_stride,
@@ -443,6 +523,19 @@ WLLM_API int wllm_rope_row_norm_kv_write(const void* qkv, int in_dtype, int row_
             (size_t)in_split_stride, (TO*)q_out, q_stride, positions, slots, inv_freq, (TO*)k_pages, (TO*)v_pages, nq, nkv, hd, \
             rot_dim, page_size, interleaved, vd, wq, wk, w_dtype, q_count, k_count, eps); \
     } while (0)
+    const bool aligned = !(((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)wq | (uintptr_t)wk) & 15);
+    if (in_dtype == WLLM_BF16 && out_dtype == WLLM_BF16 && w_dtype == WLLM_BF16 && in_splits == 1 && aligned && hd % 8 == 0 &&
+        vd % 8 == 0 && rot_dim % 8 == 0 && row_stride % 8 == 0 && q_stride % 8 == 0) {
+        static bool raised = false;
+        if (!raised && smem > 48 * 1024) {
+            const cudaError_t e = cudaFuncSetAttribute(rope_row_norm_vec_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            if (e != cudaSuccess) return 1000 + (int)e;
+            raised = true;
+        }
+        return wllm_launch(rope_row_norm_vec_kernel, n, 256, smem, stream, (const bf16*)qkv, row_stride, (bf16*)q_out, q_stride,
+                           positions, slots, inv_freq, (bf16*)k_pages, (bf16*)v_pages, nq, nkv, hd, rot_dim, page_size, interleaved,
+                           vd, (const bf16*)wq, (const bf16*)wk, q_count, k_count, eps);
+    }
     if (in_dtype == WLLM_BF16 && out_dtype == WLLM_BF16) RN(bf16, bf16);
     if (in_dtype == WLLM_F32 && out_dtype == WLLM_BF16) RN(float, bf16);
     if (in_dtype == WLLM_F32 && out_dtype == WLLM_F32) RN(float, float);

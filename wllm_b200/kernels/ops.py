@@ -296,21 +296,22 @@ def latent_prepare(fused: torch.Tensor, parts: int, positions: torch.Tensor, slo
                    dim: int, rot: int, rot_dims: int, rank: int, hd: int, pairing: str = "half") -> None:
     """From the fused projection row [heads * (dim + rot) | rank + rot] of every token (csrc/latent_attention.cu): the
     cache row [rms(latent columns) * gain | the rot columns behind them, turned | zeros] into `pages` at `slots`; the
-    queries' plain parts into `q_plain` [n, heads * dim]; their turned parts into columns rank .. of every head of
-    `q_mapped` [n, heads * hd].  Norm and turn are 32-bit, from the projection's partial sums where it left them."""
+    queries' plain parts into `q_plain` [n, heads * dim] (None: they are read where they are); their turned parts into
+    columns rank .. of every head of `q_mapped` [n, heads * hd].  Norm and turn are 32-bit, from the projection's partial sums where it left them."""
     if pairing not in ("half", "interleaved"):
         raise KernelError(f"rotary pairing {pairing!r} not supported (half, interleaved)")
     _need_cuda(fused, positions, slots, inv_freq, gain, pages, q_plain, q_mapped)
     ptr, dt, row_stride, nparts, part_stride, n = _fused_args(fused, parts)
     assert fused.shape[-1] >= heads * (dim + rot) + rank + rot and hd >= rank + rot
-    assert q_plain.shape == (n, heads * dim) and q_plain.is_contiguous() and q_mapped.shape == (n, heads * hd) and q_mapped.is_contiguous()
-    assert q_plain.dtype == q_mapped.dtype == pages.dtype and pages.is_contiguous() and pages.shape[-1] == hd and pages.shape[-3] == 1
+    assert q_mapped.shape == (n, heads * hd) and q_mapped.is_contiguous()
+    assert q_plain is None or (q_plain.shape == (n, heads * dim) and q_plain.is_contiguous() and q_plain.dtype == q_mapped.dtype)
+    assert q_mapped.dtype == pages.dtype and pages.is_contiguous() and pages.shape[-1] == hd and pages.shape[-3] == 1
     assert gain.shape == (rank,) and gain.is_contiguous()
     assert inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dims // 2 and inv_freq.is_contiguous()
     lib = load_family("latent_attention")
     _check(lib.wllm_latent_prepare(ptr, dt, row_stride, nparts, part_stride, _ptr(_int32(positions, "positions")),
                                    _ptr(_int32(slots, "slots") if slots is not None else None), _ptr(inv_freq), _ptr(gain),
-                                   _dt(gain), c_float(eps), _ptr(pages), page_size, _ptr(q_plain), _ptr(q_mapped), _dt(q_plain),
+                                   _dt(gain), c_float(eps), _ptr(pages), page_size, _ptr(q_plain), _ptr(q_mapped), _dt(q_mapped),
                                    n, heads, dim, rot, rot_dims, 1 if pairing == "interleaved" else 0, rank, hd, _stream()),
            "latent_prepare")
 

@@ -81,12 +81,15 @@ class LatentAttention:
         cols = fused if fused.shape[-1] == self.width else fused[..., col0:col0 + self.width]
         group = ctx.cache.groups[cache.group]
         pages = group.keys(cache.layer)
-        q_plain = ctx.buffer(self.tag + "latent_q_plain", (n, H * self.dim), self.model_dtype)
+        # a product that left one tensor in the model's type holds the queries' plain parts as the next product reads them
+        in_place = parts == 0 and cols.dtype == self.model_dtype
+        q_plain = None if in_place else ctx.buffer(self.tag + "latent_q_plain", (n, H * self.dim), self.model_dtype)
         q_mapped = ctx.buffer(self.tag + "latent_q", (n, H * row), self.model_dtype)
         ops.latent_prepare(cols, parts, ctx.positions, ctx.group_slots[cache.group], self.position.inv_freq, self.gain, self.eps,
                            pages, group.page_size, q_plain, q_mapped, H, self.dim, self.rot, self.position.rotary_dim, R, row,
                            pairing=getattr(self.position, "pairing", "half"))
-        ops.head_linear(q_plain.view(n, H, self.dim), self.w_uk_t, q_mapped.view(n, H, row)[:, :, :R])
+        plain = cols[:, :self.q_width].unflatten(1, (H, self.dim + self.rot))[:, :, :self.dim] if in_place else q_plain.view(n, H, self.dim)
+        ops.head_linear(plain, self.w_uk_t, q_mapped.view(n, H, row)[:, :, :R])
         mixed = ctx.buffer(self.tag + "latent_mixed", (n, H * R), self.model_dtype)
         self.attend(q_mapped, mixed, pages, ctx, cache.group)
         heads_out = ctx.buffer(self.tag + "attn", (n, H * self.vd), self.model_dtype)
