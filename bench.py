@@ -761,7 +761,7 @@ def zafilix_config(size: dict) -> dict:
     H, dim, rot, vd, rank = size["latent"]
     att = {"type": "attention", "mlp": {"kind": "dense", "ff": size["ff"]},
            "mixer": {"heads": nq, "kv_heads": nkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": size["block"]},
-                     "rot": {"dims": hd, "base": 500000.0, "scaling": {"factor": 8.0}}}}
+                     "rot": {"dims": hd, "base": 1000000.0, "scaling": {"factor": 4.0}}}}
     lat = {"type": "latent_attention", "mlp": {"kind": "dense", "ff": size["ff"]},
            "mixer": {"heads": H, "dim": dim, "rot_dim": rot, "vdim": vd, "kv_rank": rank, "scale": (dim + rot) ** -0.5,
                      "mask": {"size": size["window"]}, "rot": {"dims": rot, "base": 10000.0}}}
@@ -821,7 +821,9 @@ def zafilix_kernel_table(size: dict, pk: dict, T: int, batch: int, context: int)
         fused = rnd(n, H * (dim + rot) + row_len, dtype=bf)
         q_plain, q_mapped = torch.empty(n, H * dim, dtype=bf, device=dev), torch.empty(n, H * row_len, dtype=bf, device=dev)
         row(f"{tag}/latent row (norm, turn, cache write) and the queries' parts",
-            lambda: ops.latent_prepare(fused, 0, pos, pos, inv_rot, l_gain, 1e-6, lp, ps, q_plain, q_mapped, H, dim, rot, rot, rank, row_len),
+            # a prompt's product leaves one bfloat16 tensor: the queries' plain parts are read where they are, not copied
+            lambda: ops.latent_prepare(fused, 0, pos, pos, inv_rot, l_gain, 1e-6, lp, ps, None if tag == "prefill" else q_plain, q_mapped, H, dim,
+                                       rot, rot, rank, row_len),
             n * (H * (dim + rot) + row_len) * 2 * 2)
         w_uk, w_uv = rnd(H, rank, dim, dtype=bf, scale=0.05), rnd(H, vd, rank, dtype=bf, scale=0.05)
         mixed, heads_out = rnd(n, H, rank, dtype=bf), torch.empty(n, H, vd, dtype=bf, device=dev)

@@ -411,8 +411,8 @@ def test_rows_normed_as_wholes_then_turned_in_neighbouring_pairs(nq, nkv, hd, vd
     table = POSITIONS.build(spec("rope", theta=base, head_dim=hd, rotary_dim=rot, exact_table=True, pairing="interleaved",
                                  frequency_divisor=divisor)).inv_freq.to(DEV)
     q_gain, k_gain = (1 + 0.3 * torch.randn(nq * hd, generator=g)).to(dtype), (1 + 0.3 * torch.randn(nkv * hd, generator=g)).to(dtype)
-    for parts in (0, 3):
-        x = torch.randn(max(parts, 1), n, width + 5, generator=g) * 2
+    for parts, pad in ((0, 5), (3, 5), (0, 8)):       # a pitch in steps of 8 elements: the kernel with 16-byte accesses, where the sizes allow
+        x = torch.randn(max(parts, 1), n, width + pad, generator=g) * 2
         x = x if parts else x[0].to(dtype)
         whole = (x.double().sum(0) if parts else x.double())
         q = plain.norm_plain(whole[:, :nq * hd], q_gain.double(), eps).view(n, nq, hd)
@@ -486,6 +486,32 @@ def test_latent_row_queries_and_the_heads_maps(H, dim, rot, rank, vd, dtype):
         out = ops.head_linear(mixed.to(DEV), uv.view(H, vd, rank).contiguous().to(DEV), torch.empty(n, H, vd, dtype=dtype, device=DEV))
         want_v = torch.einsum("ihj,jhv->ihv", p, (c @ uv.double().T).view(n, H, vd))
         assert (out.cpu().double() - want_v).abs().max() < (1e-5 if dtype == torch.float32 else 0.03) * max(1.0, float(want_v.abs().max()))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,K,N", [(3, 16, 40), (2, 40, 24), (5, 10, 6), (4, 128, 512)])
+def test_heads_maps_at_every_step_size(H, K, N, dtype):
+    """y[t, h] = W_h x[t, h] from one token to hundreds (bfloat16 takes a kernel of its own for few tokens and a batched
+    product for many), x read in place from rows that hold more than x, y written into rows that hold more than y; a token's
+    result is the same, bit for bit, alone and among others of a step of the same kind."""
+    from wllm_b200.kernels import ops
+    g = torch.Generator().manual_seed(H * 100 + K)
+    w = (torch.randn(H, N, K, generator=g) * 0.2).to(dtype)
+    for n in (1, 8, 9, 31, 32, 200):
+        rows = (torch.randn(n, H * (K + 8) + 16, generator=g)).to(dtype)
+        x = rows[:, :H * (K + 8)].unflatten(1, (H, K + 8))[:, :, :K]
+        want = torch.einsum("thk,hjk->thj", x.double(), w.double())
+        held = torch.full((n, H, N + 8), float("nan"), dtype=dtype, device=DEV)
+        xd = rows.to(DEV)[:, :H * (K + 8)].unflatten(1, (H, K + 8))[:, :, :K]
+        ops.head_linear(xd, w.to(DEV), held[:, :, :N])
+        got = held[:, :, :N].cpu()
+        assert torch.isnan(held[:, :, N:]).all() and not torch.isnan(got).any()
+        tol = 2e-5 if dtype == torch.float32 else 0.02
+        assert (got.double() - want).abs().max() < tol * max(1.0, float(want.abs().max())), n
+        if n in (9, 31):       # the first token alone: the same bits (steps of the same kind)
+            alone = torch.empty(1, H, N, dtype=dtype, device=DEV)
+            ops.head_linear(xd[:1], w.to(DEV), alone)
+            assert torch.equal(alone.cpu(), got[:1]), n
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

@@ -89,13 +89,13 @@ WHOLE = {
 }
 
 _HEADS64 = [
-    {"type": "attention", "mixer": _att(4, 2, 64, None, (64, 10000.0, 4.0), 0.125, 48), "mlp": _ff(64)},
+    {"type": "attention", "mixer": _att(6, 2, 64, None, (64, 10000.0, 4.0), 0.125, 48), "mlp": _ff(64)},
     {"type": "latent_attention", "mixer": _lat(4, 32, 32, 24, 96, (32, 10000.0), 0.12, 50), "mlp": _ff(64)},
     {"type": "attention", "mixer": _att(2, 2, 64, None, (32, 500.0), 0.125, 80), "mlp": None},
 ]
 HEADS64 = {
     "architecture": "Zafilix", "vocab": 120, "width": 64, "embedding": {"scale": 4.0}, "norm": {"eps": 1e-6},
-    "logit_scale": 0.25, "logit_softcap": 12.0,
+    "logit_scale": 0.2, "logit_softcap": 12.0,
     "layers": _HEADS64 + [_again(_HEADS64, 0)],
 }
 
