@@ -1,10 +1,11 @@
 from .base import ConfigError, read_config_json
 from .engine import EngineConfig, parse_dtype
 from .gemma import GemmaConfig
+from .gudarax import GudaraxConfig
 from .pesanex import PesanexConfig
 from .taritar import TaritarConfig
 from .zafilix import ZafilixConfig
 from .registry import ARCHITECTURES, Architecture, config_from_folder, register_architecture, resolve_architecture
 
-__all__ = ["ConfigError", "read_config_json", "EngineConfig", "parse_dtype", "GemmaConfig", "PesanexConfig", "TaritarConfig", "ZafilixConfig", "ARCHITECTURES",
+__all__ = ["ConfigError", "read_config_json", "EngineConfig", "parse_dtype", "GemmaConfig", "GudaraxConfig", "PesanexConfig", "TaritarConfig", "ZafilixConfig", "ARCHITECTURES",
            "Architecture", "config_from_folder", "register_architecture", "resolve_architecture"]

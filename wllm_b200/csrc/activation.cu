@@ -151,3 +151,36 @@ WLLM_API int wllm_sigmoid_gate(void* x, int x_dtype, int x_stride, const void* g
 #undef GO
     return WLLM_BAD_DTYPE;
 }
+
+// A projection of the residual gates the token's own row of a table: out[t, c] = act(z[t, c]) * table[ids[t], c].  The
+// projection's row comes as `parts` partial sums (added in order) or as one tensor; act 0: the tanh form of GELU.  32-bit, rounded once.
+template <typename TZ, typename TT>
+__global__ void token_gate_kernel(const TZ* __restrict__ z, int z_stride, int parts, size_t part_stride, const int* __restrict__ ids,
+                                  const TT* __restrict__ table, int vocab, TT* __restrict__ out, int n, int dim) {
+    pdl_begin();
+    const size_t total = (size_t)n * dim;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / dim, c = idx % dim;
+        const TZ* src = z + t * z_stride + c;
+        float v = to_f32(src[0]);
+        for (int s = 1; s < parts; ++s) v += to_f32(src[(size_t)s * part_stride]);
+        const int id = min(max(ids[t], 0), vocab - 1);
+        const float g = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+        out[idx] = from_f32<TT>(g * to_f32(table[(size_t)id * dim + c]));
+    }
+}
+
+WLLM_API int wllm_token_gate(const void* z, int z_dtype, int z_stride, int parts, long long part_stride, const int* ids,
+                             const void* table, int t_dtype, int vocab, void* out, int act, int n, int dim, cudaStream_t stream) {
+    if (n <= 0) return WLLM_OK;
+    if (dim <= 0 || vocab <= 0 || parts < 1 || act != 0) return WLLM_BAD_SIZE;
+    const long long want = ((long long)n * dim + 255) / 256;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+#define GO(TZ, TT) wllm_launch(token_gate_kernel<TZ, TT>, blocks, 256, 0, stream, (const TZ*)z, z_stride, parts, (size_t)part_stride, ids, \
+                               (const TT*)table, vocab, (TT*)out, n, dim)
+    if (z_dtype == WLLM_BF16 && t_dtype == WLLM_BF16) return GO(bf16, bf16);
+    if (z_dtype == WLLM_F32 && t_dtype == WLLM_BF16) return GO(float, bf16);
+    if (z_dtype == WLLM_F32 && t_dtype == WLLM_F32) return GO(float, float);
+#undef GO
+    return WLLM_BAD_DTYPE;
+}

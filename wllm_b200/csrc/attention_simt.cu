@@ -38,6 +38,9 @@
 // the chunks of its kept keys (from chunk 0 on) and the chunks of its window, each once, in ascending order; tiles
 // of 32 keys without a visible key are passed by (their pages may have been given back).
 //
+// `slopes` (one 32-bit number per query head, or null): a score loses slope_h * (p - j) for the key at position j seen from
+// position p, after the scale and the cap: a bias by distance, in 32-bit from the two positions themselves.
+//
 // `v_ld`: elements between two value rows of the pool; with v_ld = hd and v_pages = k_pages the values are the first vd
 // elements of the keys' rows (a cache that holds one row per token for both).
 //
@@ -93,7 +96,7 @@ template <typename T, int NE>
 __device__ __forceinline__ void chunk_partial(const float* __restrict__ qs, const T* __restrict__ k_pages,
                                               const T* __restrict__ v_pages, const int* __restrict__ table, int nkv,
                                               int kvh, int hd, int vd, int v_ld, int page_size, int first, int kept, int pos, int chunk, float scale,
-                                              float cap, int lane, float& m, float& l, float (&o)[NE]) {
+                                              float cap, float slope, int lane, float& m, float& l, float (&o)[NE]) {
     m = -INFINITY;
     l = 0.f;
 #pragma unroll
@@ -120,6 +123,7 @@ __device__ __forceinline__ void chunk_partial(const float* __restrict__ qs, cons
             }
             s = ((acc[0] + acc[1]) + (acc[2] + acc[3])) * scale;
             if (cap > 0.f) s = cap * tanhf(s / cap);
+            if (slope != 0.f) s = __fsub_rn(s, __fmul_rn(slope, (float)(pos - key)));
         }
         const float m_new = fmaxf(m, warp_max(s));
         const float p = valid ? expf(s - m_new) : 0.f;
@@ -204,7 +208,8 @@ paged_attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict
                             const int* __restrict__ token_req, const int* __restrict__ positions,
                             const int* __restrict__ block_table, int max_pages, int n_tokens, int nq, int nkv, int hd,
                             int page_size, int window, float scale, float* __restrict__ scratch, int max_chunks,
-                            int vd, const float* __restrict__ sinks, float cap, int keep, int v_ld) {
+                            int vd, const float* __restrict__ sinks, float cap, int keep, int v_ld,
+                            const float* __restrict__ slopes) {
     extern __shared__ float q_smem[];
     pdl_begin();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -226,13 +231,14 @@ paged_attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict
     for (int d = lane; d < hd; d += 32) qs[d] = to_f32(qrow[d]);
     __syncwarp();
 
+    const float slope = slopes ? slopes[head] : 0.f;
     float m = -INFINITY, l = 0.f, o[NE];
 #pragma unroll
     for (int e = 0; e < NE; ++e) o[e] = 0.f;
     for (int slot = c0; slot <= c1; ++slot) {
         float mc, lc, oc[NE];
         chunk_partial<T, NE>(qs, k_pages, v_pages, table, nkv, kvh, hd, vd, v_ld, page_size, rk.first, rk.kept, pos, row_chunk(rk, slot),
-                             scale, cap, lane, mc, lc, oc);
+                             scale, cap, slope, lane, mc, lc, oc);
         merge_chunk<NE>(m, l, o, mc, lc, oc);
     }
     if (SPLIT) {
@@ -291,7 +297,7 @@ template <typename T>
 static int launch(const void* q, int q_stride, void* out, int out_stride, const void* k_pages, const void* v_pages,
                   const int* token_req, const int* positions, const int* block_table, int max_pages, int n_tokens,
                   int nq, int nkv, int hd, int page_size, int window, float scale, float* scratch, int max_chunks,
-                  int vd, const float* sinks, float cap, int keep, int v_ld, cudaStream_t stream) {
+                  int vd, const float* sinks, float cap, int keep, int v_ld, const float* slopes, cudaStream_t stream) {
     const int blocks = (n_tokens * nq + WARPS - 1) / WARPS;
     const size_t smem = (size_t)WARPS * hd * sizeof(float);
     const bool split = scratch != nullptr && max_chunks > 1;
@@ -299,10 +305,10 @@ static int launch(const void* q, int q_stride, void* out, int out_stride, const 
         if (!split) \
             return wllm_launch(paged_attention_simt_kernel<T, NE, false>, blocks, WARPS * 32, smem, stream, \
                 (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pages, (const T*)v_pages, token_req, positions, \
-                block_table, max_pages, n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks, cap, keep, v_ld); \
+                block_table, max_pages, n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks, cap, keep, v_ld, slopes); \
         const int st = wllm_launch(paged_attention_simt_kernel<T, NE, true>, dim3(blocks, max_chunks), WARPS * 32, smem, \
                 stream, (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pages, (const T*)v_pages, token_req, \
-                positions, block_table, max_pages, n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks, cap, keep, v_ld); \
+                positions, block_table, max_pages, n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks, cap, keep, v_ld, slopes); \
         if (st != WLLM_OK) return st; \
         return wllm_launch(paged_attention_simt_merge_kernel<T, NE>, blocks, WARPS * 32, 0, stream, (T*)out, out_stride, \
                 positions, n_tokens, nq, vd, window, (const float*)scratch, max_chunks, sinks, keep); \
@@ -323,7 +329,8 @@ WLLM_API int wllm_paged_attention_simt_strided(const void* q, int q_stride, void
                                                const void* v_pages, int dtype, const int* token_req, const int* positions,
                                                const int* block_table, int max_pages, int n_tokens, int nq, int nkv, int hd,
                                                int page_size, int window, float scale, float* scratch, int max_chunks,
-                                               int vd, const float* sinks, float cap, int keep, int v_ld, cudaStream_t stream) {
+                                               int vd, const float* sinks, float cap, int keep, int v_ld, const float* slopes,
+                                               cudaStream_t stream) {
     if (n_tokens <= 0) return WLLM_OK;
     if (v_ld == 0) v_ld = vd;
     if (v_ld < vd) return WLLM_BAD_SIZE;
@@ -336,11 +343,11 @@ WLLM_API int wllm_paged_attention_simt_strided(const void* q, int q_stride, void
     if (dtype == WLLM_BF16) {
         if (q_stride % 8 != 0) return WLLM_BAD_ALIGN;
         return launch<bf16>(q, q_stride, out, out_stride, k_pages, v_pages, token_req, positions, block_table, max_pages,
-                            n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks, cap, keep, v_ld, stream);
+                            n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks, cap, keep, v_ld, slopes, stream);
     }
     if (dtype == WLLM_F32)
         return launch<float>(q, q_stride, out, out_stride, k_pages, v_pages, token_req, positions, block_table, max_pages,
-                             n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks, cap, keep, v_ld, stream);
+                             n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks, cap, keep, v_ld, slopes, stream);
     return WLLM_BAD_DTYPE;
 }
 
@@ -351,7 +358,7 @@ WLLM_API int wllm_paged_attention_simt_general(const void* q, int q_stride, void
                                                int vd, const float* sinks, float cap, int keep, cudaStream_t stream) {
     return wllm_paged_attention_simt_strided(q, q_stride, out, out_stride, k_pages, v_pages, dtype, token_req, positions,
                                              block_table, max_pages, n_tokens, nq, nkv, hd, page_size, window, scale, scratch,
-                                             max_chunks, vd, sinks, cap, keep, 0, stream);
+                                             max_chunks, vd, sinks, cap, keep, 0, nullptr, stream);
 }
 
 WLLM_API int wllm_paged_attention_simt(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
@@ -383,7 +390,7 @@ paged_attention_simt_tiled_kernel(const T* __restrict__ q, int q_stride, T* __re
                                   const int* __restrict__ req_q_start, const int* __restrict__ req_q_len,
                                   const int* __restrict__ req_ctx_len, const int* __restrict__ block_table, int max_pages,
                                   int nq, int nkv, int hd, int page_size, int window, float scale, int vd,
-                                  const float* __restrict__ sinks, float cap, int keep, int v_ld) {
+                                  const float* __restrict__ sinks, float cap, int keep, int v_ld, const float* __restrict__ slopes) {
     constexpr int VN = Vec<T>::N;                  // elements of a 16-byte piece
     extern __shared__ __align__(16) unsigned char tl_smem[];
     pdl_begin();
@@ -401,9 +408,11 @@ paged_attention_simt_tiled_kernel(const T* __restrict__ q, int q_stride, T* __re
 
     // this warp's rows: position, first key, where they are stored
     int pos_r[TL_RPW], first_r[TL_RPW], kept_r[TL_RPW];
+    float slope_r[TL_RPW];
 #pragma unroll
     for (int i = 0; i < TL_RPW; ++i) {
         const int m = m0 + warp * TL_RPW + i;
+        slope_r[i] = slopes ? slopes[g * rep + m % rep] : 0.f;
         pos_r[i] = m < rows ? pos0 + m / rep : -1;                          // a row past the end takes no key
         const RowKeys rk = row_keys(max(pos_r[i], 0), window, keep);
         first_r[i] = rk.first;
@@ -494,6 +503,7 @@ paged_attention_simt_tiled_kernel(const T* __restrict__ q, int q_stride, T* __re
                 const bool valid = (key >= first_r[i] || key < kept_r[i]) && key <= pos_r[i];
                 float s = valid ? ((acc[i][0] + acc[i][1]) + (acc[i][2] + acc[i][3])) * scale : -INFINITY;
                 if (valid && cap > 0.f) s = cap * tanhf(s / cap);
+                if (valid && slope_r[i] != 0.f) s = __fsub_rn(s, __fmul_rn(slope_r[i], (float)(pos_r[i] - key)));
                 const float m_new = fmaxf(m_c[i], warp_max(s));
                 p[i] = valid ? expf(s - m_new) : 0.f;
                 const float corr = expf(m_c[i] - m_new);
@@ -547,7 +557,8 @@ template <typename T>
 static int launch_tiled(const void* q, int q_stride, void* out, int out_stride, const void* k_pages, const void* v_pages,
                         const int* req_q_start, const int* req_q_len, const int* req_ctx_len, const int* block_table,
                         int max_pages, int requests, int max_q_len, int nq, int nkv, int hd, int page_size, int window,
-                        float scale, int vd, const float* sinks, float cap, int keep, int v_ld, cudaStream_t stream) {
+                        float scale, int vd, const float* sinks, float cap, int keep, int v_ld, const float* slopes,
+                        cudaStream_t stream) {
     const int rep = nq / nkv;
     const dim3 grid((max_q_len * rep + TL_ROWS - 1) / TL_ROWS, nkv, requests);
     const size_t smem = (size_t)TL_ROWS * hd * sizeof(float) + 2 * 32 * ((size_t)(hd + Vec<T>::N) + vd) * sizeof(T);
@@ -561,7 +572,7 @@ static int launch_tiled(const void* q, int q_stride, void* out, int out_stride, 
         } \
         return wllm_launch(paged_attention_simt_tiled_kernel<T, NE>, grid, TL_WARPS * 32, smem, stream, (const T*)q, q_stride, \
                            (T*)out, out_stride, (const T*)k_pages, (const T*)v_pages, req_q_start, req_q_len, req_ctx_len, \
-                           block_table, max_pages, nq, nkv, hd, page_size, window, scale, vd, sinks, cap, keep, v_ld); \
+                           block_table, max_pages, nq, nkv, hd, page_size, window, scale, vd, sinks, cap, keep, v_ld, slopes); \
     } while (0)
     const int smem_max = TL_ROWS * 256 * (int)sizeof(float) + 2 * 32 * ((256 + Vec<T>::N) + 256) * (int)sizeof(T);
     if (vd <= 64) GO(2);
@@ -576,7 +587,8 @@ WLLM_API int wllm_paged_attention_simt_tiled_strided(const void* q, int q_stride
                                                      const void* v_pages, int dtype, const int* req_q_start, const int* req_q_len,
                                                      const int* req_ctx_len, const int* block_table, int max_pages, int requests,
                                                      int max_q_len, int nq, int nkv, int hd, int page_size, int window, float scale,
-                                                     int vd, const float* sinks, float cap, int keep, int v_ld, cudaStream_t stream) {
+                                                     int vd, const float* sinks, float cap, int keep, int v_ld, const float* slopes,
+                                                     cudaStream_t stream) {
     if (requests <= 0 || max_q_len <= 0) return WLLM_OK;
     if (v_ld == 0) v_ld = vd;
     if (v_ld < vd || v_ld % 8 != 0) return WLLM_BAD_SIZE;
@@ -588,12 +600,12 @@ WLLM_API int wllm_paged_attention_simt_tiled_strided(const void* q, int q_stride
         if (q_stride % 8 != 0) return WLLM_BAD_ALIGN;
         return launch_tiled<bf16>(q, q_stride, out, out_stride, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len,
                                   block_table, max_pages, requests, max_q_len, nq, nkv, hd, page_size, window, scale, vd, sinks,
-                                  cap, keep, v_ld, stream);
+                                  cap, keep, v_ld, slopes, stream);
     }
     if (dtype == WLLM_F32)
         return launch_tiled<float>(q, q_stride, out, out_stride, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len,
                                    block_table, max_pages, requests, max_q_len, nq, nkv, hd, page_size, window, scale, vd, sinks,
-                                   cap, keep, v_ld, stream);
+                                   cap, keep, v_ld, slopes, stream);
     return WLLM_BAD_DTYPE;
 }
 
@@ -604,7 +616,7 @@ WLLM_API int wllm_paged_attention_simt_tiled_general(const void* q, int q_stride
                                                      int vd, const float* sinks, float cap, int keep, cudaStream_t stream) {
     return wllm_paged_attention_simt_tiled_strided(q, q_stride, out, out_stride, k_pages, v_pages, dtype, req_q_start, req_q_len,
                                                    req_ctx_len, block_table, max_pages, requests, max_q_len, nq, nkv, hd, page_size,
-                                                   window, scale, vd, sinks, cap, keep, 0, stream);
+                                                   window, scale, vd, sinks, cap, keep, 0, nullptr, stream);
 }
 
 WLLM_API int wllm_paged_attention_simt_tiled(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,

@@ -853,13 +853,13 @@ static int launch_grouped(const CUtensorMap& ma, const CUtensorMap& mw, void* c,
 }
 
 // The experts' products: a [rows, K] bf16 rows sorted by expert, w [experts * w_rows, K] (w_rows = N, or 2 N = [gate; up] with the
-// gated epilogue 5), c [rows, N] (32-bit with epilogue 1, bf16 with 0 and 5), tiles: the table of row tiles on the device (at most
+// gated epilogue 5), c [rows, N] (32-bit with epilogue 1, bf16 with 0, 5 and 6 = relu(.)^2), tiles: the table of row tiles on the device (at most
 // max_row_tiles of them).  K in steps of 8.
 WLLM_API int wllm_gemm_bf16_tc_grouped(const void* a, int lda, const void* w, int ldw, void* c, int ldc, int rows, int N, int K,
                                        int experts, int epilogue, const int* tiles, int max_row_tiles, int* status, int max_ctas,
                                        float p0, float p1, cudaStream_t stream) {
     if (rows <= 0 || N <= 0) return WLLM_OK;
-    if (epilogue != EPI_BF16 && epilogue != EPI_F32 && epilogue != EPI_GATED_CAPPED) return WLLM_BAD_SIZE;
+    if (epilogue != EPI_BF16 && epilogue != EPI_F32 && epilogue != EPI_GATED_CAPPED && epilogue != EPI_RELU_SQUARED) return WLLM_BAD_SIZE;
     if (K <= 0 || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || lda < K || ldw < K || experts < 1 || max_row_tiles < 1) return WLLM_BAD_SIZE;
     if (((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)c & 15) || tiles == nullptr) return WLLM_BAD_ALIGN;
     const bool gated = epilogue == EPI_GATED_CAPPED;
@@ -877,6 +877,7 @@ WLLM_API int wllm_gemm_bf16_tc_grouped(const void* a, int lda, const void* w, in
         case EPI_BF16: return launch_grouped<EPI_BF16>(ma, mw, c, ldc, N, K, w_rows, 0, half_rows, tiles, status, ctas, stream, ep);
         case EPI_F32: return launch_grouped<EPI_F32>(ma, mw, c, ldc, N, K, w_rows, 0, half_rows, tiles, status, ctas, stream, ep);
         case EPI_GATED_CAPPED: return launch_grouped<EPI_GATED_CAPPED>(ma, mw, c, ldc, N, K, w_rows, N, half_rows, tiles, status, ctas, stream, ep);
+        case EPI_RELU_SQUARED: return launch_grouped<EPI_RELU_SQUARED>(ma, mw, c, ldc, N, K, w_rows, 0, half_rows, tiles, status, ctas, stream, ep);
     }
     return WLLM_BAD_SIZE;
 }

@@ -21,15 +21,18 @@ __device__ __forceinline__ float value_at(const void* p, int dtype, size_t i) {
     return dtype == WLLM_BF16 ? __bfloat162float(reinterpret_cast<const bf16*>(p)[i]) : reinterpret_cast<const float*>(p)[i];
 }
 
-// fused row: [heads * (dim + rot) query columns | rank + rot down-projection columns] from column 0 of `fused`
+// fused row: [heads * (dim + rot) query columns | rank + rot down-projection columns] from column 0 of `fused`.
+// With a latent row of the queries (q_rank > 0, no turning part): [q_rank columns | rank down-projection columns]; the first
+// run is normed like the cache row, with a gain of its own, and goes to `cq_out` [n, q_rank] for the product that makes the
+// queries; nothing of the queries is laid out here but the zeros behind every head's mapped part.
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(256)
 latent_prepare_kernel(const TI* __restrict__ fused, int row_stride, int in_splits, size_t in_split_stride,
                       const int* __restrict__ positions, const int* __restrict__ slots, const float* __restrict__ inv_freq,
                       const void* __restrict__ gain, int gain_dtype, float eps, TO* __restrict__ pages, int page_size,
                       TO* __restrict__ q_plain, TO* __restrict__ q_mapped, int heads, int dim, int rot, int rot_dims,
-                      int interleaved, int rank, int hd) {
-    extern __shared__ float sm[];             // [rank] the latent columns, [half] sines, [half] cosines
+                      int interleaved, int rank, int hd, int q_rank, const void* __restrict__ q_gain, TO* __restrict__ cq_out) {
+    extern __shared__ float sm[];             // [rank] the latent columns, [half] sines, [half] cosines, [q_rank] the queries' latent columns
     __shared__ float scratch[32];
     pdl_launch_dependents();
     const int t = blockIdx.x;
@@ -54,7 +57,20 @@ latent_prepare_kernel(const TI* __restrict__ fused, int row_stride, int in_split
         }
         return v;
     };
-    const int qw = heads * (dim + rot);
+    const int qw = q_rank > 0 ? q_rank : heads * (dim + rot);
+    if (q_rank > 0) {
+        float* qs = cs + half;
+        float sq = 0.f;
+        for (int c = threadIdx.x; c < q_rank; c += blockDim.x) {
+            const float v = in(c);
+            qs[c] = v;
+            sq += v * v;
+        }
+        sq = block_sum(sq, scratch);
+        const float inv_q = 1.0f / sqrtf(sq / (float)q_rank + eps);
+        for (int c = threadIdx.x; c < q_rank; c += blockDim.x)
+            cq_out[(size_t)t * q_rank + c] = from_f32<TO>((qs[c] * inv_q) * value_at(q_gain, gain_dtype, c));
+    }
     float ss = 0.f;
     for (int c = threadIdx.x; c < rank; c += blockDim.x) {
         const float v = in(qw + c);
@@ -81,7 +97,7 @@ latent_prepare_kernel(const TI* __restrict__ fused, int row_stride, int in_split
         for (int e = threadIdx.x; e < hd - rank; e += blockDim.x)
             dst[rank + e] = e < rot ? from_f32<TO>(turned([&](int i) { return in(qw + rank + i); }, e)) : from_f32<TO>(0.f);
     }
-    if (q_plain != nullptr)                   // null: the next product reads the plain parts from the fused row itself
+    if (q_plain != nullptr && q_rank == 0)    // null: the next product reads the plain parts from the fused row itself
         for (int item = threadIdx.x; item < heads * dim; item += blockDim.x) {
             const int h = item / dim, c = item % dim;
             q_plain[(size_t)t * heads * dim + item] = from_f32<TO>(in(h * (dim + rot) + c));
@@ -100,18 +116,19 @@ latent_prepare_kernel(const TI* __restrict__ fused, int row_stride, int in_split
 WLLM_API int wllm_latent_prepare(const void* fused, int in_dtype, int row_stride, int in_splits, long long in_split_stride,
                                  const int* positions, const int* slots, const float* inv_freq, const void* gain, int gain_dtype,
                                  float eps, void* pages, int page_size, void* q_plain, void* q_mapped, int out_dtype, int n,
-                                 int heads, int dim, int rot, int rot_dims, int interleaved, int rank, int hd,
-                                 cudaStream_t stream) {
+                                 int heads, int dim, int rot, int rot_dims, int interleaved, int rank, int hd, int q_rank,
+                                 const void* q_gain, void* cq_out, cudaStream_t stream) {
     if (n <= 0) return WLLM_OK;
     if (heads <= 0 || dim <= 0 || rot < 0 || rot_dims < 0 || rot_dims > rot || (rot_dims & 1) || rank <= 0 || hd < rank + rot ||
         page_size <= 0 || in_splits < 1)
         return WLLM_BAD_SIZE;
+    if (q_rank < 0 || (q_rank > 0 && (rot != 0 || q_gain == nullptr || cq_out == nullptr))) return WLLM_BAD_SIZE;
     if (gain_dtype != WLLM_BF16 && gain_dtype != WLLM_F32) return WLLM_BAD_DTYPE;
-    const size_t smem = ((size_t)rank + rot_dims) * sizeof(float);
+    const size_t smem = ((size_t)rank + rot_dims + q_rank) * sizeof(float);
     if (smem > 48 * 1024) return WLLM_BAD_SIZE;
 #define GO(TI, TO) wllm_launch(latent_prepare_kernel<TI, TO>, n, 256, smem, stream, (const TI*)fused, row_stride, in_splits, \
         (size_t)in_split_stride, positions, slots, inv_freq, gain, gain_dtype, eps, (TO*)pages, page_size, (TO*)q_plain, \
-        (TO*)q_mapped, heads, dim, rot, rot_dims, interleaved, rank, hd)
+        (TO*)q_mapped, heads, dim, rot, rot_dims, interleaved, rank, hd, q_rank, q_gain, (TO*)cq_out)
     if (in_dtype == WLLM_BF16 && out_dtype == WLLM_BF16) return GO(bf16, bf16);
     if (in_dtype == WLLM_F32 && out_dtype == WLLM_BF16) return GO(float, bf16);
     if (in_dtype == WLLM_F32 && out_dtype == WLLM_F32) return GO(float, float);

@@ -17,6 +17,10 @@
 //            tokens' rows copied into sorted order (moe_gather) and the table of row tiles that the plan writes.
 //   combine  out[token] = sum over the token's ranks, in rank order, of weight * y[place] (+ gate * shared unit).
 //
+// Two more forms.  Scores: softmax over all experts, or (score_mode 1) sigmoid(z) expert by expert, not normalised.  Unit
+// (MODE 2): an expert without a gate, down(relu(up (s a))^2), whose input is multiplied by the pair's score s: the up product
+// is linear, so s multiplies its 32-bit sums in front of the activation; the combine then adds the experts' outputs as they are.
+//
 // The gated unit is the clamped one: g = min(gate, limit), u = clamp(up, -limit, limit), g sigmoid(slope g) (u + 1).
 #include "common.cuh"
 
@@ -28,7 +32,7 @@ template <typename T>
 __global__ void __launch_bounds__(1024)
 moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w_router, const float* __restrict__ w_gate,
                  int* __restrict__ chosen, float* __restrict__ weights, float* __restrict__ gate_out, int n, int H, int E, int top,
-                 int groups, int groups_kept, int tpb) {
+                 int groups, int groups_kept, int tpb, int score_mode) {
     extern __shared__ float route_smem[];          // [tpb][H] the tokens' rows, [tpb][E] scores, [tpb][groups] group scores
     float* hs_all = route_smem;
     float* sc_all = hs_all + (size_t)tpb * H;
@@ -80,14 +84,18 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w_router, co
         const int t = t0 + j;
         float* sc = sc_all + (size_t)j * E;
         float* gs = gs_all + (size_t)j * groups;
-        float m = -INFINITY;
-        for (int e = lane; e < E; e += 32) m = fmaxf(m, sc[e]);
-        m = warp_max(m);
-        float sum = 0.f;
-        for (int e = lane; e < E; e += 32) { const float p = expf(sc[e] - m); sc[e] = p; sum += p; }
-        sum = warp_sum(sum);
-        const float inv = 1.0f / sum;
-        for (int e = lane; e < E; e += 32) sc[e] *= inv;
+        if (score_mode == 1) {
+            for (int e = lane; e < E; e += 32) sc[e] = 1.0f / (1.0f + expf(-sc[e]));
+        } else {
+            float m = -INFINITY;
+            for (int e = lane; e < E; e += 32) m = fmaxf(m, sc[e]);
+            m = warp_max(m);
+            float sum = 0.f;
+            for (int e = lane; e < E; e += 32) { const float p = expf(sc[e] - m); sc[e] = p; sum += p; }
+            sum = warp_sum(sum);
+            const float inv = 1.0f / sum;
+            for (int e = lane; e < E; e += 32) sc[e] *= inv;
+        }
         __syncwarp();
         const int per = E / groups;
         for (int g = lane; g < groups; g += 32) {
@@ -213,10 +221,13 @@ constexpr int GM = 32, GN = 64, GK = 16;
 // One tile of rows (of one expert) by one tile of columns.  GATED: w holds [E][2 N][K] (gate rows, then up rows), the
 // rows of a are gathered (token = sorted[r] / top) and out[r][c] = unit(gate, up) in TO; else w is [E][N][K], the rows
 // of a are the sorted rows and out is 32-bit.  Thread (ty, tx) of 16 x 16 owns rows ty, ty + 16 and columns tx + 16 j.
-template <typename T, typename TO, bool GATED>
+// MODE 2: w is [E][N][K], the rows of a are gathered as for the gated unit, and out[r][c] = relu(row_w[sorted[r]] * sum)^2 in TO.
+template <typename T, typename TO, int MODE>
 __global__ void __launch_bounds__(256)
 moe_grouped_kernel(const T* __restrict__ a, int a_stride, const T* __restrict__ w, TO* __restrict__ out, int N, int K,
-                   const int* __restrict__ offset, const int* __restrict__ sorted, int E, int top, float limit, float slope) {
+                   const int* __restrict__ offset, const int* __restrict__ sorted, int E, int top, float limit, float slope,
+                   const float* __restrict__ row_w) {
+    constexpr bool GATED = MODE == 1, GATHER = MODE != 0;
     __shared__ float As[GK][GM + 1];
     __shared__ float Ws[GATED ? 2 : 1][GK][GN + 1];
     __shared__ int s_expert, s_row0, s_rows;
@@ -247,7 +258,7 @@ moe_grouped_kernel(const T* __restrict__ a, int a_stride, const T* __restrict__ 
     // which row of `a` each of the tile's rows reads
     const int lr = threadIdx.x >> 3;                 // 0..31: the row this thread loads (two k each)
     int src_row = -1;
-    if (lr < rows) src_row = GATED ? sorted[row0 + lr] / top : row0 + lr;
+    if (lr < rows) src_row = GATHER ? sorted[row0 + lr] / top : row0 + lr;
     for (int k0 = 0; k0 < K; k0 += GK) {
         {
             const int kk = (threadIdx.x & 7) * 2;
@@ -291,6 +302,10 @@ moe_grouped_kernel(const T* __restrict__ a, int a_stride, const T* __restrict__ 
             if (GATED) {
                 const float g = fminf(v, limit), u = fminf(fmaxf(acc[GATED ? 1 : 0][i][j], -limit), limit);
                 v = (g / (1.0f + expf(-slope * g))) * (u + 1.0f);
+            }
+            if (MODE == 2) {
+                v = fmaxf(row_w ? v * row_w[sorted[row0 + r]] : v, 0.f);
+                v *= v;
             }
             out[(size_t)(row0 + r) * N + col] = from_f32<TO>(v);
         }
@@ -345,10 +360,12 @@ __device__ __forceinline__ void moe_find_tile(const int* __restrict__ offset, in
     }
 }
 
-template <typename TO, bool GATED>
+template <typename TO, int MODE>
 __global__ void __launch_bounds__(256)
 moe_grouped_mma_kernel(const bf16* __restrict__ a, int a_stride, const bf16* __restrict__ w, TO* __restrict__ out, int N, int K,
-                       const int* __restrict__ offset, const int* __restrict__ sorted, int E, int top, float limit, float slope) {
+                       const int* __restrict__ offset, const int* __restrict__ sorted, int E, int top, float limit, float slope,
+                       const float* __restrict__ row_w) {
+    constexpr bool GATED = MODE == 1, GATHER = MODE != 0;
     extern __shared__ __align__(16) unsigned char moe_smem[];
     bf16 (*As)[TM][TPITCH] = reinterpret_cast<bf16 (*)[TM][TPITCH]>(moe_smem);
     bf16 (*Ws)[TN][TPITCH] = reinterpret_cast<bf16 (*)[TN][TPITCH]>(moe_smem + TSTAGES * TM * TPITCH * 2);
@@ -370,7 +387,7 @@ moe_grouped_mma_kernel(const bf16* __restrict__ a, int a_stride, const bf16* __r
     // what this thread copies a stage: TK / 32 16-byte pieces of a row of A (64 rows) and of two rows of W (128 rows)
     const int a_row = threadIdx.x >> 2, piece0 = threadIdx.x & 3;
     const bf16* a_src = nullptr;
-    if (a_row < rows) a_src = a + (size_t)(GATED ? sorted[row0 + a_row] / top : row0 + a_row) * a_stride;
+    if (a_row < rows) a_src = a + (size_t)(GATHER ? sorted[row0 + a_row] / top : row0 + a_row) * a_stride;
     const bf16* w_src[2];
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
@@ -435,6 +452,7 @@ moe_grouped_mma_kernel(const bf16* __restrict__ a, int a_stride, const bf16* __r
             const int r = wm * 32 + mi * 16 + (lane >> 2) + half * 8;
             if (r >= rows) continue;
             TO* orow = out + (size_t)(row0 + r) * N;
+            const float rw = (MODE == 2 && row_w) ? row_w[sorted[row0 + r]] : 1.0f;
 #pragma unroll
             for (int ni = 0; ni < (GATED ? 2 : 4); ++ni)
 #pragma unroll
@@ -446,6 +464,7 @@ moe_grouped_mma_kernel(const bf16* __restrict__ a, int a_stride, const bf16* __r
                         const float g = fminf(v, limit), u = fminf(fmaxf(acc[mi][ni + 2][half * 2 + c], -limit), limit);
                         v = (g / (1.0f + expf(-slope * g))) * (u + 1.0f);
                     }
+                    if (MODE == 2) { v = fmaxf(v * rw, 0.f); v *= v; }
                     orow[col] = from_f32<TO>(v);
                 }
         }
@@ -465,7 +484,7 @@ moe_combine_rows_kernel(const float* __restrict__ y, const int* __restrict__ pla
         float v = 0.f;
         for (int k = 0; k < top; ++k) {
             // every product and sum rounded on its own, in both kernels: one result whichever serves the row
-            const float term = __fmul_rn(weights[(size_t)t * top + k], y[(size_t)place[(size_t)t * top + k] * H + c]);
+            const float term = __fmul_rn(weights ? weights[(size_t)t * top + k] : 1.0f, y[(size_t)place[(size_t)t * top + k] * H + c]);
             v = k == 0 ? term : __fadd_rn(v, term);
         }
         if (shared != nullptr) {
@@ -491,7 +510,7 @@ moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place, c
     __shared__ float s_weight[64];
     pdl_begin();
     const int t = blockIdx.x;
-    for (int k = threadIdx.x; k < min(top, 64); k += blockDim.x) { s_place[k] = place[(size_t)t * top + k]; s_weight[k] = weights[(size_t)t * top + k]; }
+    for (int k = threadIdx.x; k < min(top, 64); k += blockDim.x) { s_place[k] = place[(size_t)t * top + k]; s_weight[k] = weights ? weights[(size_t)t * top + k] : 1.0f; }
     __syncthreads();
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
         float v = 0.f;
@@ -503,7 +522,7 @@ moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place, c
                 term[u] = 0.f;
                 if (k < top) {
                     const int row = k < 64 ? s_place[k] : place[(size_t)t * top + k];
-                    const float wk = k < 64 ? s_weight[k] : weights[(size_t)t * top + k];
+                    const float wk = k < 64 ? s_weight[k] : (weights ? weights[(size_t)t * top + k] : 1.0f);
                     term[u] = __fmul_rn(wk, y[(size_t)row * H + c]);
                 }
             }
@@ -528,8 +547,10 @@ moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place, c
 }
 
 WLLM_API int wllm_moe_route(const void* h, int dtype, const float* w_router, const float* w_gate, int* chosen, float* weights,
-                            float* gate_out, int n, int H, int E, int top, int groups, int groups_kept, cudaStream_t stream) {
+                            float* gate_out, int n, int H, int E, int top, int groups, int groups_kept, int score_mode,
+                            cudaStream_t stream) {
     if (n <= 0) return WLLM_OK;
+    if (score_mode != 0 && score_mode != 1) return WLLM_BAD_SIZE;
     if (H <= 0 || E <= 0 || E > MOE_MAX_EXPERTS || top < 1 || groups < 1 || E % groups != 0 || groups_kept < 1 ||
         groups_kept > groups || top > groups_kept * (E / groups) || (w_gate != nullptr && gate_out == nullptr))
         return WLLM_BAD_SIZE;
@@ -546,7 +567,7 @@ WLLM_API int wllm_moe_route(const void* h, int dtype, const float* w_router, con
             if (er != cudaSuccess) return 1000 + (int)er; \
         } \
         return wllm_launch(moe_route_kernel<T>, (n + tpb - 1) / tpb, threads, smem, stream, (const T*)h, w_router, w_gate, chosen, weights, \
-                           gate_out, n, H, E, top, groups, groups_kept, tpb); \
+                           gate_out, n, H, E, top, groups, groups_kept, tpb, score_mode); \
     } while (0)
     if (dtype == WLLM_BF16) GO(bf16);
     if (dtype == WLLM_F32) GO(float);
@@ -577,52 +598,80 @@ WLLM_API int wllm_moe_plan(const int* chosen, int pairs, int E, int* count, int*
 }
 
 // out[r] = x[sorted[r] / top]: the tokens' rows in the order of the sorted pairs (K elements of 2 bytes, K in steps of 8)
+// row_w (null: none): the row is multiplied by its pair's weight on the way, in 32-bit, rounded once
 __global__ void __launch_bounds__(128) moe_gather_kernel(const bf16* __restrict__ x, int x_stride, const int* __restrict__ sorted, int top,
-                                                         bf16* __restrict__ out, int K) {
+                                                         bf16* __restrict__ out, int K, const float* __restrict__ row_w) {
     pdl_begin();
     const int r = blockIdx.x;
     const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(sorted[r] / top) * x_stride);
     uint4* dst = reinterpret_cast<uint4*>(out + (size_t)r * K);
-    for (int i = threadIdx.x; i < K / 8; i += blockDim.x) dst[i] = src[i];
+    if (row_w == nullptr) {
+        for (int i = threadIdx.x; i < K / 8; i += blockDim.x) dst[i] = src[i];
+        return;
+    }
+    const float s = row_w[sorted[r]];
+    for (int i = threadIdx.x; i < K / 8; i += blockDim.x) {
+        uint4 v = src[i];
+        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h2[e]);
+            h2[e] = __floats2bfloat162_rn(f.x * s, f.y * s);
+        }
+        dst[i] = v;
+    }
 }
 
-WLLM_API int wllm_moe_gather(const void* x, int x_stride, const int* sorted, int top, void* out, int pairs, int K, cudaStream_t stream) {
+WLLM_API int wllm_moe_gather_scaled(const void* x, int x_stride, const int* sorted, int top, void* out, int pairs, int K,
+                                    const float* row_w, cudaStream_t stream) {
     if (pairs <= 0) return WLLM_OK;
     if (K <= 0 || K % 8 != 0 || x_stride % 8 != 0 || top < 1) return WLLM_BAD_SIZE;
     if (((uintptr_t)x & 15) || ((uintptr_t)out & 15)) return WLLM_BAD_ALIGN;
-    return wllm_launch(moe_gather_kernel, pairs, 128, 0, stream, (const bf16*)x, x_stride, sorted, top, (bf16*)out, K);
+    return wllm_launch(moe_gather_kernel, pairs, 128, 0, stream, (const bf16*)x, x_stride, sorted, top, (bf16*)out, K, row_w);
 }
 
-// gated = 1: a [n][K] rows of tokens (stride a_stride), w [E][2 N][K], out [pairs][N] of the operands' type;
-// gated = 0: a [pairs][K] sorted rows, w [E][N][K], out [pairs][N] 32-bit.
-WLLM_API int wllm_moe_grouped(const void* a, int a_stride, const void* w, void* out, int dtype, int gated, int pairs, int N, int K,
-                              const int* offset, const int* sorted, int E, int top, float limit, float slope, cudaStream_t stream) {
+WLLM_API int wllm_moe_gather(const void* x, int x_stride, const int* sorted, int top, void* out, int pairs, int K, cudaStream_t stream) {
+    return wllm_moe_gather_scaled(x, x_stride, sorted, top, out, pairs, K, nullptr, stream);
+}
+
+// unit = 1: a [n][K] rows of tokens (stride a_stride), w [E][2 N][K], out [pairs][N] of the operands' type (the clamped gated unit);
+// unit = 0: a [pairs][K] sorted rows, w [E][N][K], out [pairs][N] 32-bit;
+// unit = 2: a [n][K] rows of tokens, w [E][N][K], out [pairs][N] of the operands' type = relu(row_w[pair] * (w a))^2 (row_w null: 1).
+WLLM_API int wllm_moe_grouped_unit(const void* a, int a_stride, const void* w, void* out, int dtype, int unit, int pairs, int N, int K,
+                                   const int* offset, const int* sorted, int E, int top, float limit, float slope, const float* row_w,
+                                   cudaStream_t stream) {
     if (pairs <= 0) return WLLM_OK;
-    if (N <= 0 || K <= 0 || E <= 0 || E > MOE_MAX_EXPERTS || top < 1) return WLLM_BAD_SIZE;
+    if (N <= 0 || K <= 0 || E <= 0 || E > MOE_MAX_EXPERTS || top < 1 || unit < 0 || unit > 2) return WLLM_BAD_SIZE;
     const dim3 grid((N + GN - 1) / GN, (pairs + GM - 1) / GM + E);
     if (grid.y > 65535) return WLLM_BAD_SIZE;
-#define GO(T, TO, G) wllm_launch(moe_grouped_kernel<T, TO, G>, grid, 256, 0, stream, (const T*)a, a_stride, (const T*)w, (TO*)out, N, K, \
-                                 offset, sorted, E, top, limit, slope)
+#define GO(T, TO, M) wllm_launch(moe_grouped_kernel<T, TO, M>, grid, 256, 0, stream, (const T*)a, a_stride, (const T*)w, (TO*)out, N, K, \
+                                 offset, sorted, E, top, limit, slope, row_w)
     if (dtype == WLLM_BF16 && K % 8 == 0 && a_stride % 8 == 0 && !((uintptr_t)a & 15) && !((uintptr_t)w & 15)) {
-        const dim3 tgrid((N + (gated ? TN / 2 : TN) - 1) / (gated ? TN / 2 : TN), (pairs + TM - 1) / TM + E);
+        const int cols = unit == 1 ? TN / 2 : TN;
+        const dim3 tgrid((N + cols - 1) / cols, (pairs + TM - 1) / TM + E);
         if (tgrid.y > 65535) return WLLM_BAD_SIZE;
         static bool raised = false;
         if (!raised) {
-            cudaError_t er = cudaFuncSetAttribute(moe_grouped_mma_kernel<bf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, T_SMEM);
-            if (er == cudaSuccess) er = cudaFuncSetAttribute(moe_grouped_mma_kernel<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, T_SMEM);
+            cudaError_t er = cudaFuncSetAttribute(moe_grouped_mma_kernel<bf16, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, T_SMEM);
+            if (er == cudaSuccess) er = cudaFuncSetAttribute(moe_grouped_mma_kernel<float, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, T_SMEM);
+            if (er == cudaSuccess) er = cudaFuncSetAttribute(moe_grouped_mma_kernel<bf16, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, T_SMEM);
             if (er != cudaSuccess) return 1000 + (int)er;
             raised = true;
         }
-        if (gated)
-            return wllm_launch(moe_grouped_mma_kernel<bf16, true>, tgrid, 256, T_SMEM, stream, (const bf16*)a, a_stride, (const bf16*)w,
-                               (bf16*)out, N, K, offset, sorted, E, top, limit, slope);
-        return wllm_launch(moe_grouped_mma_kernel<float, false>, tgrid, 256, T_SMEM, stream, (const bf16*)a, a_stride, (const bf16*)w,
-                           (float*)out, N, K, offset, sorted, E, top, limit, slope);
+#define TGO(TO, M) wllm_launch(moe_grouped_mma_kernel<TO, M>, tgrid, 256, T_SMEM, stream, (const bf16*)a, a_stride, (const bf16*)w, \
+                               (TO*)out, N, K, offset, sorted, E, top, limit, slope, row_w)
+        return unit == 1 ? TGO(bf16, 1) : unit == 2 ? TGO(bf16, 2) : TGO(float, 0);
+#undef TGO
     }
-    if (dtype == WLLM_BF16) return gated ? GO(bf16, bf16, true) : GO(bf16, float, false);
-    if (dtype == WLLM_F32) return gated ? GO(float, float, true) : GO(float, float, false);
+    if (dtype == WLLM_BF16) return unit == 1 ? GO(bf16, bf16, 1) : unit == 2 ? GO(bf16, bf16, 2) : GO(bf16, float, 0);
+    if (dtype == WLLM_F32) return unit == 1 ? GO(float, float, 1) : unit == 2 ? GO(float, float, 2) : GO(float, float, 0);
 #undef GO
     return WLLM_BAD_DTYPE;
+}
+
+WLLM_API int wllm_moe_grouped(const void* a, int a_stride, const void* w, void* out, int dtype, int gated, int pairs, int N, int K,
+                              const int* offset, const int* sorted, int E, int top, float limit, float slope, cudaStream_t stream) {
+    return wllm_moe_grouped_unit(a, a_stride, w, out, dtype, gated ? 1 : 0, pairs, N, K, offset, sorted, E, top, limit, slope, nullptr, stream);
 }
 
 WLLM_API int wllm_moe_combine(const float* y, const int* place, const float* weights, int top, const void* shared, int shared_dtype,

@@ -16,6 +16,8 @@
 //
 // With row gains (`wllm_rope_row_norm_kv_write`) the query row and the key row of a token are normed as wholes, all heads at
 // once, in front of the turn: q <- q / sqrt(mean(q^2) + eps) * wq over the token's nq * hd query elements, the same for k.
+// There the projections may have a bias (one 32-bit row for q | k | v, added to the finished sums, in front of the norms), and
+// the values may be blended with an earlier layer's values of the same token before they are cached.
 //
 // Page layout: [page][kv_head][slot_in_page][head_dim] (values: [..][vd]); `slots[n]` is page * page_size + slot_in_page.
 #include "common.cuh"
@@ -351,7 +353,8 @@ rope_row_norm_kernel(const TI* __restrict__ qkv, int row_stride, int in_splits, 
                      const int* __restrict__ slots, const float* __restrict__ inv_freq,
                      TO* __restrict__ k_pages, TO* __restrict__ v_pages, int nq, int nkv, int hd,
                      int rot_dim, int page_size, int interleaved, int vd, const void* __restrict__ wq,
-                     const void* __restrict__ wk, int w_dtype, int q_count, int k_count, float eps) {
+                     const void* __restrict__ wk, int w_dtype, int q_count, int k_count, float eps,
+                     const float* __restrict__ bias, float* __restrict__ v_first, const float* __restrict__ lam, int mix_mode) {
     extern __shared__ float row[];            // [(nq + nkv) * hd] the token's q and k parts, [half] sines, [half] cosines
     __shared__ float scratch[32];
     pdl_launch_dependents();
@@ -364,7 +367,7 @@ rope_row_norm_kernel(const TI* __restrict__ qkv, int row_stride, int in_splits, 
     for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf(pos * inv_freq[j], &sn[j], &cs[j]);
     pdl_wait();
     const TI* x = qkv + (size_t)t * row_stride;
-    auto in = [&](int c) {     // part 0 + part 1 + ... in order; sixteen loads are in flight at a time
+    auto sum_in = [&](int c) {     // part 0 + part 1 + ... in order; sixteen loads are in flight at a time
         if (in_splits == 1) return to_f32(x[c]);
         float v = 0.f;
         for (int sp = 0; sp < in_splits; sp += 16) {
@@ -377,6 +380,7 @@ rope_row_norm_kernel(const TI* __restrict__ qkv, int row_stride, int in_splits, 
         }
         return v;
     };
+    auto in = [&](int c) { return bias ? sum_in(c) + bias[c] : sum_in(c); };      // the projection's bias joins the finished sum
     float ssq = 0.f, ssk = 0.f;
     for (int c = threadIdx.x; c < qw + kw; c += blockDim.x) {
         const float v = in(c);
@@ -411,9 +415,15 @@ rope_row_norm_kernel(const TI* __restrict__ qkv, int row_stride, int in_splits, 
         dst_of(h)[c] = from_f32<TO>(normed(h, c));
     }
     if (slot < 0) return;
+    // mix_mode 1: the token's values are left in v_first [n, nkv * vd] for the layers behind this one; 2: the cached values
+    // are (1 - lam) v + lam v_first, in 32-bit, rounded once
+    const float l = mix_mode == 2 ? lam[0] : 0.f;
     for (int item = threadIdx.x; item < nkv * vd; item += blockDim.x) {
         const int kvh = item / vd, c = item % vd;
-        v_pages[(((size_t)(slot / page_size) * nkv + kvh) * page_size + slot % page_size) * vd + c] = from_f32<TO>(in(qw + kw + item));
+        float v = in(qw + kw + item);
+        if (mix_mode == 1) v_first[(size_t)t * nkv * vd + item] = v;
+        else if (mix_mode == 2) v = fmaf(l, v_first[(size_t)t * nkv * vd + item], (1.0f - l) * v);
+        v_pages[(((size_t)(slot / page_size) * nkv + kvh) * page_size + slot % page_size) * vd + c] = from_f32<TO>(v);
     }
 }
 
@@ -503,8 +513,11 @@ WLLM_API int wllm_rope_row_norm_kv_write(const void* qkv, int in_dtype, int row_
                                          void* q_out, int out_dtype, int q_stride, const int* positions, const int* slots,
                                          const float* inv_freq, void* k_pages, void* v_pages, int n, int nq, int nkv, int hd,
                                          int rot_dim, int page_size, int interleaved, int vd, const void* wq, const void* wk,
-                                         int w_dtype, int q_count, int k_count, float eps, cudaStream_t stream) {
+                                         int w_dtype, int q_count, int k_count, float eps, const float* bias, float* v_first,
+                                         const float* lam, int mix_mode, cudaStream_t stream) {
     if (n <= 0) return WLLM_OK;
+    if (mix_mode < 0 || mix_mode > 2 || (mix_mode > 0 && (v_first == nullptr || slots == nullptr)) || (mix_mode == 2 && lam == nullptr))
+        return WLLM_BAD_SIZE;
     if (hd <= 0 || vd <= 0 || rot_dim < 0 || rot_dim > hd || (rot_dim & 1) || page_size <= 0 || nq <= 0 || nkv < 0 ||
         (nkv == 0 && slots != nullptr) || in_splits < 1 || q_count <= 0 || (nkv > 0 && k_count <= 0) || wq == nullptr ||
         (nkv > 0 && wk == nullptr))
@@ -521,10 +534,10 @@ WLLM_API int wllm_rope_row_norm_kv_write(const void* qkv, int in_dtype, int row_
         } \
         return wllm_launch(rope_row_norm_kernel<TI, TO>, n, 256, smem, stream, (const TI*)qkv, row_stride, in_splits, \
             (size_t)in_split_stride, (TO*)q_out, q_stride, positions, slots, inv_freq, (TO*)k_pages, (TO*)v_pages, nq, nkv, hd, \
-            rot_dim, page_size, interleaved, vd, wq, wk, w_dtype, q_count, k_count, eps); \
+            rot_dim, page_size, interleaved, vd, wq, wk, w_dtype, q_count, k_count, eps, bias, v_first, lam, mix_mode); \
     } while (0)
     const bool aligned = !(((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)wq | (uintptr_t)wk) & 15);
-    if (in_dtype == WLLM_BF16 && out_dtype == WLLM_BF16 && w_dtype == WLLM_BF16 && in_splits == 1 && aligned && hd % 8 == 0 &&
+    if (bias == nullptr && mix_mode == 0 && in_dtype == WLLM_BF16 && out_dtype == WLLM_BF16 && w_dtype == WLLM_BF16 && in_splits == 1 && aligned && hd % 8 == 0 &&
         vd % 8 == 0 && rot_dim % 8 == 0 && row_stride % 8 == 0 && q_stride % 8 == 0) {
         static bool raised = false;
         if (!raised && smem > 48 * 1024) {

@@ -13,6 +13,7 @@ FAMILIES = {
     "attention_simt": [{}],
     "activation": [{}],
     "linear_attention": [{}],
+    "delta_rule": [{}],
     "latent_attention": [{}],
     "hyper_connections": [{}],
     "moe": [{}],

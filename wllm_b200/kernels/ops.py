@@ -265,11 +265,14 @@ def rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, positions: torch.Tenso
 def rope_row_norm_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor, slots, inv_freq: torch.Tensor,
                            k_pages, v_pages, nq: int, nkv: int, hd: int, rot_dim: int, page_size: int, q_gain: torch.Tensor,
                            k_gain: torch.Tensor, eps: float, q_count: int, k_count: int, in_splits: int = 0,
-                           pairing: str = "half", vd: int | None = None) -> None:
+                           pairing: str = "half", vd: int | None = None, bias: torch.Tensor | None = None,
+                           v_first: torch.Tensor | None = None, blend: torch.Tensor | None = None, mix: str | None = None) -> None:
     """As rope_kv_write, with the token's query row and key row normed as wholes (all heads at once) in front of the
     turn: q <- q / sqrt(mean(q^2) + eps) * q_gain over the nq * hd query elements, the same for k with k_gain
     (csrc/rope_cache.cu).  `q_count`, `k_count`: the elements that count for the means (heads held in steps of 8
-    elements carry zeros behind them)."""
+    elements carry zeros behind them).  `bias`: one float32 row [(nq + nkv) * hd + nkv * vd] added to the projections' sums
+    in front of the norms.  `mix` 'first': the token's values are also left in `v_first` [n, nkv * vd] float32; 'later': the
+    values that are cached are (1 - blend[0]) v + blend[0] v_first."""
     if pairing not in ("half", "interleaved"):
         raise KernelError(f"rotary pairing {pairing!r} not supported (half, interleaved)")
     _need_cuda(qkv, q_out, positions, slots, inv_freq, k_pages, v_pages, q_gain, k_gain)
@@ -282,27 +285,43 @@ def rope_row_norm_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, positions: to
     assert q_gain.is_contiguous() and k_gain.is_contiguous()
     if slots is not None:
         assert k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == q_out.dtype == v_pages.dtype
+    if mix not in (None, "first", "later"):
+        raise KernelError(f"value mixing {mix!r}: 'first' or 'later'")
+    _need_cuda(bias, v_first, blend)
+    assert bias is None or (bias.dtype == torch.float32 and bias.shape == (width,) and bias.is_contiguous())
+    if mix is not None:
+        assert v_first.dtype == torch.float32 and v_first.shape == (n, nkv * vd) and v_first.is_contiguous()
+        assert mix == "first" or (blend.dtype == torch.float32 and blend.numel() == 1)
     lib = load_family("rope_cache")
     _check(lib.wllm_rope_row_norm_kv_write(ptr, dt, row_stride, nparts, part_stride, _ptr(q_out), _dt(q_out), q_out.stride(0),
                                            _ptr(_int32(positions, "positions")),
                                            _ptr(_int32(slots, "slots") if slots is not None else None), _ptr(inv_freq),
                                            _ptr(k_pages), _ptr(v_pages), n, nq, nkv, hd, rot_dim, page_size,
                                            1 if pairing == "interleaved" else 0, vd, _ptr(q_gain), _ptr(k_gain), _dt(q_gain),
-                                           q_count, k_count, c_float(eps), _stream()), "rope_row_norm_kv_write")
+                                           q_count, k_count, c_float(eps), _ptr(bias), _ptr(v_first if mix is not None else None),
+                                           _ptr(blend if mix == "later" else None), {None: 0, "first": 1, "later": 2}[mix],
+                                           _stream()), "rope_row_norm_kv_write")
 
 
 def latent_prepare(fused: torch.Tensor, parts: int, positions: torch.Tensor, slots, inv_freq: torch.Tensor, gain: torch.Tensor,
                    eps: float, pages: torch.Tensor, page_size: int, q_plain: torch.Tensor, q_mapped: torch.Tensor, heads: int,
-                   dim: int, rot: int, rot_dims: int, rank: int, hd: int, pairing: str = "half") -> None:
+                   dim: int, rot: int, rot_dims: int, rank: int, hd: int, pairing: str = "half", q_rank: int = 0,
+                   q_gain: torch.Tensor | None = None, cq_out: torch.Tensor | None = None) -> None:
     """From the fused projection row [heads * (dim + rot) | rank + rot] of every token (csrc/latent_attention.cu): the
     cache row [rms(latent columns) * gain | the rot columns behind them, turned | zeros] into `pages` at `slots`; the
     queries' plain parts into `q_plain` [n, heads * dim] (None: they are read where they are); their turned parts into
-    columns rank .. of every head of `q_mapped` [n, heads * hd].  Norm and turn are 32-bit, from the projection's partial sums where it left them."""
+    columns rank .. of every head of `q_mapped` [n, heads * hd].  Norm and turn are 32-bit, from the projection's partial sums where it left them.
+    With `q_rank` > 0 the row is [q_rank | rank] instead (queries that pass a latent row of their own; nothing turns): those
+    columns, normed with `q_gain` [q_rank], go to `cq_out` [n, q_rank] for the product that makes the queries."""
     if pairing not in ("half", "interleaved"):
         raise KernelError(f"rotary pairing {pairing!r} not supported (half, interleaved)")
     _need_cuda(fused, positions, slots, inv_freq, gain, pages, q_plain, q_mapped)
     ptr, dt, row_stride, nparts, part_stride, n = _fused_args(fused, parts)
-    assert fused.shape[-1] >= heads * (dim + rot) + rank + rot and hd >= rank + rot
+    assert fused.shape[-1] >= (q_rank if q_rank else heads * (dim + rot)) + rank + rot and hd >= rank + rot
+    _need_cuda(q_gain, cq_out)
+    if q_rank:
+        assert rot == 0 and q_gain.shape == (q_rank,) and q_gain.is_contiguous() and q_gain.dtype == gain.dtype
+        assert cq_out.shape == (n, q_rank) and cq_out.is_contiguous() and cq_out.dtype == q_mapped.dtype
     assert q_mapped.shape == (n, heads * hd) and q_mapped.is_contiguous()
     assert q_plain is None or (q_plain.shape == (n, heads * dim) and q_plain.is_contiguous() and q_plain.dtype == q_mapped.dtype)
     assert q_mapped.dtype == pages.dtype and pages.is_contiguous() and pages.shape[-1] == hd and pages.shape[-3] == 1
@@ -312,7 +331,8 @@ def latent_prepare(fused: torch.Tensor, parts: int, positions: torch.Tensor, slo
     _check(lib.wllm_latent_prepare(ptr, dt, row_stride, nparts, part_stride, _ptr(_int32(positions, "positions")),
                                    _ptr(_int32(slots, "slots") if slots is not None else None), _ptr(inv_freq), _ptr(gain),
                                    _dt(gain), c_float(eps), _ptr(pages), page_size, _ptr(q_plain), _ptr(q_mapped), _dt(q_mapped),
-                                   n, heads, dim, rot, rot_dims, 1 if pairing == "interleaved" else 0, rank, hd, _stream()),
+                                   n, heads, dim, rot, rot_dims, 1 if pairing == "interleaved" else 0, rank, hd, q_rank,
+                                   _ptr(q_gain if q_rank else None), _ptr(cq_out if q_rank else None), _stream()),
            "latent_prepare")
 
 
@@ -419,14 +439,15 @@ def paged_attention_simt(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tens
                          nq: int, nkv: int, hd: int, page_size: int, window: int, scale: float,
                          scratch: torch.Tensor | None = None, max_chunks: int = 0, vd: int | None = None,
                          sinks: torch.Tensor | None = None, cap: float = 0.0, keep: int = 0,
-                         values_in_keys: bool = False) -> torch.Tensor:
+                         values_in_keys: bool = False, slopes: torch.Tensor | None = None) -> torch.Tensor:
     """q: [n, nq*hd] view (row stride free); pages: [num_pages, nkv, page_size, hd]; out: [n, nq*hd].
     `window` > 0: a row sees itself and the window - 1 keys before it; < 0: the earlier keys of its own block of -window
     positions (blocks counted from position 0); 0: every earlier key.  `values_in_keys`: a token's value is the first vd
     elements of its key's row (`v_pages` is `k_pages`).
     `vd`: size of a value head when it is not hd (value pages [.., vd], out [n, nq*vd]); `sinks`: float32 [nq], one
     more term e^(sink) in every row's softmax denominator.  `cap` > 0: scores become cap * tanh(score / cap);
-    `keep` > 0 (with a window): the sequence's first `keep` keys stay visible behind the window.
+    `keep` > 0 (with a window): the sequence's first `keep` keys stay visible behind the window.  `slopes`: float32 [nq]; the
+    score of key j from position p loses slopes[head] * (p - j), after the scale and the cap.
     With `scratch` (float32, n * nq * max_chunks * (hd + 2) floats) and max_chunks = simt_chunks(...) > 1 every
     (row, chunk of 64 keys) gets a warp of its own and a second kernel merges them; the result is the same,
     bit for bit, as without."""
@@ -438,6 +459,7 @@ def paged_attention_simt(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tens
     assert k_pages.shape[-1] == hd and v_pages.shape[-1] == (hd if values_in_keys else vd)
     assert not values_in_keys or (v_pages.data_ptr() == k_pages.data_ptr() and vd <= hd)
     assert sinks is None or (sinks.dtype == torch.float32 and sinks.shape == (nq,) and sinks.is_contiguous())
+    assert slopes is None or (slopes.is_cuda and slopes.dtype == torch.float32 and slopes.shape == (nq,) and slopes.is_contiguous())
     if scratch is not None:
         assert scratch.dtype == torch.float32 and scratch.is_contiguous() and max_chunks >= 1
         assert scratch.numel() >= n * nq * max_chunks * (vd + 2)
@@ -447,7 +469,7 @@ def paged_attention_simt(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tens
                                                  _ptr(_int32(positions, "positions")), _ptr(_int32(block_table, "block_table")),
                                                  block_table.shape[1], n, nq, nkv, hd, page_size, window, c_float(scale),
                                                  _ptr(scratch), max_chunks if scratch is not None else 0, vd, _ptr(sinks),
-                                                 c_float(cap), keep, hd if values_in_keys else 0, _stream()),
+                                                 c_float(cap), keep, hd if values_in_keys else 0, _ptr(slopes), _stream()),
            f"paged_attention_simt(head_dim={hd}/{vd}, heads={nq}/{nkv})")
     if scratch is not None and max_chunks > 1:
         global launches
@@ -460,7 +482,7 @@ def paged_attention_simt_tiled(q: torch.Tensor, out: torch.Tensor, k_pages: torc
                                block_table: torch.Tensor, max_q_len: int, nq: int, nkv: int, hd: int, page_size: int,
                                window: int, scale: float, vd: int | None = None,
                                sinks: torch.Tensor | None = None, cap: float = 0.0, keep: int = 0,
-                               values_in_keys: bool = False) -> torch.Tensor:
+                               values_in_keys: bool = False, slopes: torch.Tensor | None = None) -> torch.Tensor:
     """The same attention as `paged_attention_simt`, bit for bit, for steps that bring portions of prompts: a CTA
     takes 32 rows of one (request, key/value head) and reads every tile of keys and values once for all of them
     (csrc/attention_simt.cu, tiled).  Head sizes up to 256; requests are given by their start, length and context."""
@@ -471,6 +493,7 @@ def paged_attention_simt_tiled(q: torch.Tensor, out: torch.Tensor, k_pages: torc
     assert k_pages.shape[-1] == hd and v_pages.shape[-1] == (hd if values_in_keys else vd)
     assert not values_in_keys or (v_pages.data_ptr() == k_pages.data_ptr() and vd <= hd)
     assert sinks is None or (sinks.dtype == torch.float32 and sinks.shape == (nq,) and sinks.is_contiguous())
+    assert slopes is None or (slopes.is_cuda and slopes.dtype == torch.float32 and slopes.shape == (nq,) and slopes.is_contiguous())
     lib = load_family("attention_simt")
     _check(lib.wllm_paged_attention_simt_tiled_strided(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages),
                                                        _ptr(v_pages), _dt(q), _ptr(_int32(req_q_start, "req_q_start")),
@@ -479,7 +502,7 @@ def paged_attention_simt_tiled(q: torch.Tensor, out: torch.Tensor, k_pages: torc
                                                        _ptr(_int32(block_table, "block_table")), block_table.shape[1],
                                                        req_q_len.shape[0], max_q_len, nq, nkv, hd, page_size, window,
                                                        c_float(scale), vd, _ptr(sinks), c_float(cap), keep,
-                                                       hd if values_in_keys else 0, _stream()),
+                                                       hd if values_in_keys else 0, _ptr(slopes), _stream()),
            f"paged_attention_simt_tiled(head_dim={hd}/{vd}, heads={nq}/{nkv})")
     return out
 
@@ -683,6 +706,25 @@ def sigmoid_gate(x: torch.Tensor, fused: torch.Tensor, parts: int, col0: int) ->
     _check(lib.wllm_sigmoid_gate(_ptr(x), _dt(x), x.stride(0), c_void_p(fused.data_ptr() + col0 * item), dt, row_stride, nparts,
                                  part_stride, n, width, _stream()), "sigmoid_gate")
     return x
+
+
+TOKEN_GATE_ACTIVATIONS = {"gelu_tanh": 0}
+
+
+def token_gate(z: torch.Tensor, parts: int, token_ids: torch.Tensor, table: torch.Tensor, act: str, out: torch.Tensor) -> torch.Tensor:
+    """out[n, c] = act(z[n, c]) * table[token_ids[n], c]: a projection of the residual gates the token's own table row.  `z` is
+    [n, dim] (or float32 partial sums [parts, n, dim], added in order); the activation and the product are 32-bit, rounded once."""
+    if act not in TOKEN_GATE_ACTIVATIONS:
+        raise KernelError(f"activation {act!r} not supported ({', '.join(TOKEN_GATE_ACTIVATIONS)})")
+    _need_cuda(z, token_ids, table, out)
+    ptr, dt, row_stride, nparts, part_stride, n = _fused_args(z, parts)
+    V, dim = table.shape
+    assert table.is_contiguous() and out.shape == (n, dim) and out.is_contiguous() and out.dtype == table.dtype
+    assert z.shape[-1] == dim and token_ids.shape[0] == n
+    lib = load_family("activation")
+    _check(lib.wllm_token_gate(ptr, dt, row_stride, nparts, part_stride, _ptr(_int32(token_ids, "token_ids")), _ptr(table), _dt(table),
+                               V, _ptr(out), TOKEN_GATE_ACTIVATIONS[act], n, dim, _stream()), "token_gate")
+    return out
 
 
 def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -1033,9 +1075,69 @@ def head_gate_norm(o: torch.Tensor, fused, parts: int, gate_off: int, weight, ep
     return out
 
 
+def delta_prepare(fused, parts: int, offsets: dict, heads: int, kv_heads: int, dim: int, vdim: int, taps: int, conv_q, conv_k,
+                  conv_v, a_log, dt_bias, token_req, req_q_start, req_slot, conv_state, unit_eps: float, q_scale: float, q, k, v,
+                  beta, decay) -> None:
+    """What enters the gated delta rule, from the fused projection [n, W] (or float32 partial sums [parts, n, W]) whose columns
+    `offsets` names (q, k, v, b, a): q, k [n, kv_heads, dim] and v [n, heads, vdim] through their short convolutions (taps
+    [channels, taps], the last tap the token's own; the inputs before a portion's start come from `conv_state`
+    [slots, taps - 1, channels]) and SiLU, q and k divided by sqrt(sum(x^2) + unit_eps) per head (q also times q_scale),
+    beta = sigmoid(b) and decay = exp(-exp(a_log) softplus(a + dt_bias)) [n, heads]; all 32-bit (csrc/delta_rule.cu)."""
+    _need_cuda(fused, conv_q, conv_k, conv_v, a_log, dt_bias, token_req, req_q_start, req_slot, conv_state, q, k, v, beta, decay)
+    ptr, dt, row_stride, nparts, part_stride, n = _fused_args(fused, parts)
+    C = 2 * kv_heads * dim + heads * vdim
+    assert conv_q.shape == conv_k.shape == (kv_heads * dim, taps) and conv_v.shape == (heads * vdim, taps)
+    assert conv_q.dtype == conv_k.dtype == conv_v.dtype == a_log.dtype == dt_bias.dtype
+    assert all(t.is_contiguous() for t in (conv_q, conv_k, conv_v, a_log, dt_bias, q, k, v, beta, decay))
+    assert a_log.shape == dt_bias.shape == (heads,)
+    assert q.shape == k.shape == (n, kv_heads * dim) and v.shape == (n, heads * vdim) and beta.shape == decay.shape == (n, heads)
+    assert all(t.dtype == torch.float32 for t in (q, k, v, beta, decay))
+    assert taps == 1 or (conv_state.dtype == torch.float32 and conv_state.is_contiguous() and conv_state.shape[1:] == (taps - 1, C))
+    lib = load_family("delta_rule")
+    _check(lib.wllm_delta_prepare(ptr, dt, row_stride, nparts, part_stride, offsets["q"], offsets["k"], offsets["v"], offsets["b"],
+                                  offsets["a"], n, heads, kv_heads, dim, vdim, taps, _ptr(conv_q), _ptr(conv_k), _ptr(conv_v),
+                                  _ptr(a_log), _ptr(dt_bias), _dt(conv_q), _ptr(_int32(token_req, "token_req")),
+                                  _ptr(_int32(req_q_start, "req_q_start")), _ptr(_int32(req_slot, "req_slot")),
+                                  _ptr(conv_state if taps > 1 else None), c_float(unit_eps), c_float(q_scale), _ptr(q), _ptr(k), _ptr(v),
+                                  _ptr(beta), _ptr(decay), _stream()), "delta_prepare")
+
+
+def delta_conv_update(fused, parts: int, offsets: dict, heads: int, kv_heads: int, dim: int, vdim: int, taps: int, req_q_start,
+                      req_q_len, req_slot, conv_state) -> None:
+    """The last taps - 1 inputs of the short convolutions, per request, after this step's tokens: conv_state[slot] becomes the
+    tail of (what it held, the step's q | k | v columns of `fused`).  Requests that bring no token are passed by."""
+    if taps <= 1:
+        return
+    _need_cuda(fused, req_q_start, req_q_len, req_slot, conv_state)
+    ptr, dt, row_stride, nparts, part_stride, _ = _fused_args(fused, parts)
+    lib = load_family("delta_rule")
+    _check(lib.wllm_delta_conv_update(ptr, dt, row_stride, nparts, part_stride, offsets["q"], offsets["k"], offsets["v"], heads,
+                                      kv_heads, dim, vdim, taps, _ptr(_int32(req_q_start, "req_q_start")),
+                                      _ptr(_int32(req_q_len, "req_q_len")), _ptr(_int32(req_slot, "req_slot")), req_q_len.shape[0],
+                                      _ptr(conv_state), _stream()), "delta_conv_update")
+
+
+def delta_scan(q, k, v, beta, decay, state, out, req_q_start, req_q_len, req_slot, heads: int, kv_heads: int, dim: int, vdim: int):
+    """The gated delta rule over every request's tokens of the step, in order, from and to its state slot:
+    S <- decay S; u = beta (v - S^T k); S <- S + k u^T; out = S^T q.  q, k [n, kv_heads * dim], v, out [n, heads * vdim],
+    beta, decay [n, heads], state [slots, heads, dim, vdim], all float32 (csrc/delta_rule.cu)."""
+    _need_cuda(q, k, v, beta, decay, state, out, req_q_start, req_q_len, req_slot)
+    n = q.shape[0]
+    assert all(t.dtype == torch.float32 and t.is_contiguous() for t in (q, k, v, beta, decay, state, out))
+    assert q.shape == k.shape == (n, kv_heads * dim) and v.shape == out.shape == (n, heads * vdim) and beta.shape == decay.shape == (n, heads)
+    assert state.shape[1:] == (heads, dim, vdim)
+    lib = load_family("delta_rule")
+    _check(lib.wllm_delta_scan(_ptr(q), _ptr(k), _ptr(v), _ptr(beta), _ptr(decay), _ptr(state), _ptr(out),
+                               _ptr(_int32(req_q_start, "req_q_start")), _ptr(_int32(req_q_len, "req_q_len")),
+                               _ptr(_int32(req_slot, "req_slot")), req_q_len.shape[0], heads, kv_heads, dim, vdim, _stream()),
+           f"delta_scan(heads={heads}/{kv_heads}, dim={dim}/{vdim})")
+    return out
+
+
 def moe_route(x: torch.Tensor, w_router: torch.Tensor, w_gate, chosen: torch.Tensor, weights: torch.Tensor, gate_out,
-              groups: int = 1, groups_kept: int = 1) -> None:
-    """The router of routed experts (csrc/moe.cu): scores = softmax(w_router x) in 32-bit over all E experts, the choice
+              groups: int = 1, groups_kept: int = 1, scores: str = "softmax") -> None:
+    """The router of routed experts (csrc/moe.cu): scores = softmax(w_router x) in 32-bit over all E experts (`scores`
+    'sigmoid': sigmoid(w_router x) expert by expert, not normalised), the choice
     limited to the `groups_kept` best of `groups` groups of neighbouring experts; chosen [n, top] (descending score) and
     weights [n, top] (the scores as they are).  With `w_gate` [H], gate_out[n] = sigmoid(w_gate . x)."""
     _need_cuda(x, w_router, w_gate, chosen, weights, gate_out)
@@ -1047,9 +1149,11 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, w_gate, chosen: torch.Ten
     if w_gate is not None:
         assert w_gate.dtype == torch.float32 and w_gate.shape == (H,) and w_gate.is_contiguous()
         assert gate_out.dtype == torch.float32 and gate_out.shape == (n,) and gate_out.is_contiguous()
+    if scores not in ("softmax", "sigmoid"):
+        raise KernelError(f"router scores {scores!r}: 'softmax' or 'sigmoid'")
     lib = load_family("moe")
     _check(lib.wllm_moe_route(_ptr(x), _dt(x), _ptr(w_router), _ptr(w_gate), _ptr(chosen), _ptr(weights), _ptr(gate_out), n, H, E,
-                              top, groups, groups_kept, _stream()), f"moe_route(experts={E}, top={top}, groups={groups}/{groups_kept})")
+                              top, groups, groups_kept, 1 if scores == "sigmoid" else 0, _stream()), f"moe_route(experts={E}, top={top}, groups={groups}/{groups_kept})")
 
 
 MOE_TILE_ROWS = 128      # rows of a row tile of the experts' products on the tensor-memory kernel
@@ -1084,30 +1188,40 @@ def moe_plan(chosen: torch.Tensor, count: torch.Tensor, offset: torch.Tensor, or
 
 
 def moe_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offset: torch.Tensor, order: torch.Tensor, top: int,
-                gated: bool, limit: float = 0.0, slope: float = 0.0) -> torch.Tensor:
+                gated: bool, limit: float = 0.0, slope: float = 0.0, unit: str | None = None,
+                row_weights: torch.Tensor | None = None) -> torch.Tensor:
     """The experts' products over rows sorted by expert.  gated: a [n, K] holds the tokens' rows (sorted row r reads row
     order[r] // top), w [E, 2N, K] = [gate; up] per expert, out [pairs, N] = the clamped gated unit, in the operands' type.
+    `unit` 'relu_squared' (not gated): a [n, K] holds the tokens' rows too, w [E, N, K], out [pairs, N] = relu(s (w a))^2 in the
+    operands' type, s = row_weights[pair] (float32 [pairs] in pair order; None: 1).
     Otherwise a [pairs, K] holds sorted rows, w [E, N, K], out [pairs, N] float32.  32-bit accumulation."""
-    _need_cuda(a, w, out, offset, order)
+    _need_cuda(a, w, out, offset, order, row_weights)
+    if unit not in (None, "relu_squared") or (unit is not None and gated):
+        raise KernelError(f"expert unit {unit!r}: None or 'relu_squared', and not gated")
     E, pairs, K = w.shape[0], order.shape[0], a.shape[1]
     N = w.shape[1] // 2 if gated else w.shape[1]
+    gathers = gated or unit is not None
     assert a.dtype == w.dtype and a.stride(1) == 1 and w.is_contiguous() and w.shape[2] == K and out.is_contiguous()
-    assert out.shape == (pairs, N) and out.dtype == (a.dtype if gated else torch.float32) and offset.shape == (E + 1,)
-    assert gated or a.shape[0] == pairs
+    assert out.shape == (pairs, N) and out.dtype == (a.dtype if gathers else torch.float32) and offset.shape == (E + 1,)
+    assert gathers or a.shape[0] == pairs
+    assert row_weights is None or (unit is not None and row_weights.dtype == torch.float32 and row_weights.numel() == pairs and row_weights.is_contiguous())
     lib = load_family("moe")
-    _check(lib.wllm_moe_grouped(_ptr(a), a.stride(0), _ptr(w), _ptr(out), _dt(a), 1 if gated else 0, pairs, N, K,
-                                _ptr(_int32(offset, "offset")), _ptr(_int32(order, "order")), E, top, c_float(limit), c_float(slope),
-                                _stream()), f"moe_grouped({pairs}x{N}x{K}, {E} experts)")
+    _check(lib.wllm_moe_grouped_unit(_ptr(a), a.stride(0), _ptr(w), _ptr(out), _dt(a), 1 if gated else (2 if unit else 0), pairs, N, K,
+                                     _ptr(_int32(offset, "offset")), _ptr(_int32(order, "order")), E, top, c_float(limit), c_float(slope),
+                                     _ptr(row_weights), _stream()), f"moe_grouped({pairs}x{N}x{K}, {E} experts)")
     return out
 
 
-def moe_gather(x: torch.Tensor, order: torch.Tensor, top: int, out: torch.Tensor) -> torch.Tensor:
-    """out[r] = x[order[r] // top]: the tokens' bfloat16 rows in the order of the sorted pairs."""
-    _need_cuda(x, order, out)
+def moe_gather(x: torch.Tensor, order: torch.Tensor, top: int, out: torch.Tensor, row_weights: torch.Tensor | None = None) -> torch.Tensor:
+    """out[r] = x[order[r] // top]: the tokens' bfloat16 rows in the order of the sorted pairs; with `row_weights` (float32
+    [pairs], pair order) every row is multiplied by its pair's weight, in 32-bit, rounded once."""
+    _need_cuda(x, order, out, row_weights)
     pairs, K = out.shape
     assert x.dtype == out.dtype == torch.bfloat16 and x.stride(1) == 1 and out.is_contiguous() and x.shape[1] == K and order.shape == (pairs,)
+    assert row_weights is None or (row_weights.dtype == torch.float32 and row_weights.numel() == pairs and row_weights.is_contiguous())
     lib = load_family("moe")
-    _check(lib.wllm_moe_gather(_ptr(x), x.stride(0), _ptr(_int32(order, "order")), top, _ptr(out), pairs, K, _stream()), "moe_gather")
+    _check(lib.wllm_moe_gather_scaled(_ptr(x), x.stride(0), _ptr(_int32(order, "order")), top, _ptr(out), pairs, K, _ptr(row_weights),
+                                      _stream()), "moe_gather")
     return out
 
 
@@ -1118,20 +1232,22 @@ def tc_grouped_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def gemm_bf16_tc_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tiles: torch.Tensor, gated: bool, limit: float = 0.0,
-                         slope: float = 0.0) -> torch.Tensor:
+                         slope: float = 0.0, unit: str | None = None) -> torch.Tensor:
     """The experts' products on tcgen05 tensor cores (csrc/gemm_bf16_tc.cu, grouped): a [rows, K] bfloat16 rows sorted by
     expert, w [E, N, K] (or, gated, [E, 2N, K] = [gate; up]: out = the clamped gated unit, bfloat16 [rows, N]; else out float32
-    [rows, N]), `tiles` the table of row tiles that moe_plan left on the device."""
+    [rows, N]; `unit` 'relu_squared': out = relu(a w^T)^2, bfloat16), `tiles` the table of row tiles that moe_plan left on the device."""
     _need_cuda(a, w, out, tiles)
     if not tc_grouped_ok(a, w):
         raise KernelError("gemm_bf16_tc_grouped: contiguous bfloat16 operands with K in steps of 8")
     rows, K = a.shape
     E = w.shape[0]
     N = w.shape[1] // 2 if gated else w.shape[1]
-    assert out.shape == (rows, N) and out.is_contiguous() and out.dtype == (torch.bfloat16 if gated else torch.float32)
+    if unit not in (None, "relu_squared") or (unit is not None and gated):
+        raise KernelError(f"expert unit {unit!r}: None or 'relu_squared', and not gated")
+    assert out.shape == (rows, N) and out.is_contiguous() and out.dtype == (torch.bfloat16 if gated or unit else torch.float32)
     assert tiles.dtype == torch.int32 and tiles.numel() >= 1 + 3 * moe_row_tiles(rows, E)
     lib = load_family("gemm_bf16_tc")
-    _check(lib.wllm_gemm_bf16_tc_grouped(_ptr(a), K, _ptr(w), K, _ptr(out), N, rows, N, K, E, 5 if gated else 1, _ptr(tiles),
+    _check(lib.wllm_gemm_bf16_tc_grouped(_ptr(a), K, _ptr(w), K, _ptr(out), N, rows, N, K, E, 5 if gated else (6 if unit else 1), _ptr(tiles),
                                          moe_row_tiles(rows, E), _ptr(_status_word(a.device)), sm_count(), c_float(limit),
                                          c_float(slope), _stream()), f"gemm_bf16_tc_grouped({rows}x{N}x{K}, {E} experts)")
     return out
@@ -1139,12 +1255,12 @@ def gemm_bf16_tc_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, ti
 
 def moe_combine(y: torch.Tensor, place: torch.Tensor, weights: torch.Tensor, shared, gate, out: torch.Tensor) -> torch.Tensor:
     """out[t] = sum over ranks k, in order, of weights[t, k] * y[place[t * top + k]]  (+ gate[t] * shared[t]; `shared`:
-    None or (tensor [n, H] | float32 partial sums [P, n, H], P or 0))."""
+    None or (tensor [n, H] | float32 partial sums [P, n, H], P or 0)).  `weights` None: the outputs are added as they are."""
     _need_cuda(y, place, weights, gate, out, shared[0] if shared is not None else None)
-    n, top = weights.shape
-    H = y.shape[1]
-    assert y.dtype == torch.float32 == out.dtype and y.is_contiguous() and out.is_contiguous() and out.shape == (n, H)
-    assert place.shape == (n * top,) and weights.dtype == torch.float32 and weights.is_contiguous()
+    n, H = out.shape
+    top = place.shape[0] // max(n, 1)
+    assert y.dtype == torch.float32 == out.dtype and y.is_contiguous() and out.is_contiguous() and y.shape[1] == H
+    assert place.shape == (n * top,) and (weights is None or (weights.shape == (n, top) and weights.dtype == torch.float32 and weights.is_contiguous()))
     ps = _branch_args(shared, n, H) if shared is not None else (_ptr(None), _F32, 1, ctypes.c_longlong(0))
     lib = load_family("moe")
     _check(lib.wllm_moe_combine(_ptr(y), _ptr(_int32(place, "place")), _ptr(weights), top, *ps, _ptr(gate), _ptr(out), n, H,

@@ -1,2 +1,2 @@
 """Built-in architectures: importing this package registers them."""
-from . import gemma, pesanex, taritar, zafilix  # noqa: F401
+from . import gemma, gudarax, pesanex, taritar, zafilix  # noqa: F401

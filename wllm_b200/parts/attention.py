@@ -22,7 +22,12 @@ counted from position 0 of the sequence), row_norm ({"q": name, "k": name, "eps"
 heads at once, is divided by its root mean square and multiplied by the gain of that name, the key row likewise, in
 front of the rotary turn), gate_proj (checkpoint name of a matrix [num_heads * value_dim, hidden]: the heads' outputs are
 multiplied by the sigmoid of that projection of the mixer's input before the output projection; the gate is computed by
-the same product as q, k and v).
+the same product as q, k and v), bias ({"q": name, "k": name, "v": name}: a bias row per projection, added to the
+finished sums in 32-bit; with row_norm), distance_slopes (one number per query head: the score of key j from position i
+loses slope_h * (i - j), after the scale and the cap), value_mix ({"weight": name, "role": 'first' | 'later', "key":
+label}: the layers that share a label blend their values with those of the layer whose role is 'first', for the same
+token: v <- (1 - w) v + w v_first with w the scalar tensor `weight`, in 32-bit; the blended values are what is cached.  The
+first layer leaves its values in a buffer of the step; its own `weight` tensor is read and not used).
 
 A mixer may be one of several that read the same input (a block that runs two mixers side
 by side): `input_weights()` lists the matrices that read the input, `mix(fused, parts,
@@ -68,6 +73,16 @@ class PagedAttention:
             raise ValueError("a mask of blocks keeps no first keys and reads no other run's cache")
         self.row_norm = spec.options.get("row_norm")
         self.gate_name = spec.options.get("gate_proj")
+        self.bias_names = spec.options.get("bias")
+        slopes = spec.options.get("distance_slopes")
+        self.slope_values = None if slopes is None else [float(v) for v in slopes]
+        self.value_mix = spec.options.get("value_mix")
+        if self.value_mix is not None and self.value_mix["role"] not in ("first", "later"):
+            raise ValueError(f"value_mix role {self.value_mix['role']!r}: 'first' or 'later'")
+        if (self.bias_names is not None or self.value_mix is not None) and (self.row_norm is None or self.borrows):
+            raise ValueError("projection biases and blended values are built into the kernel that norms q and k as whole rows (row_norm)")
+        if self.slope_values is not None and len(self.slope_values) != self.nq:
+            raise ValueError(f"{len(self.slope_values)} distance slopes for {self.nq} query heads")
         if self.row_norm is not None and self.borrows:
             raise ValueError("row norms of q and k need the mixer's own key projection")
         self.position = POSITIONS.build(spec.position)
@@ -83,14 +98,14 @@ class PagedAttention:
             raise ValueError(f"head size {self.hd_file}: heads that are divided by their root mean square come in steps of 8 elements")
         self.sink_name = spec.options.get("sink")
         self.unit_norm_eps = spec.options.get("qk_unit_norm_eps")
-        # the tensor-core kernels take keys and values of one size; other cases run on the general kernels
-        self.general = self.vd != self.hd
+        # the tensor-core kernels take keys and values of one size and no bias by distance; other cases run on the general kernels
+        self.general = self.vd != self.hd or self.slope_values is not None
         # columns of the fused q|k|v row (q alone in a mixer that reads another's keys and values), the gate's behind them
         self.qkv_width = self.nq * self.hd if self.borrows else (self.nq + self.nkv) * self.hd + self.nkv * self.vd
         self.width = self.qkv_width + (self.nq * self.vd if self.gate_name is not None else 0)
         self.q_gain = self.k_gain = None
         self.tag = ""                    # set by a mixer that runs this one beside another: keeps their buffers apart
-        self.wqkv = self.wo = self.sinks = None
+        self.wqkv = self.wo = self.sinks = self.bias = self.slopes = self.blend = None
 
     def cache_need(self):
         return KVNeed(self.nkv, self.hd, self.window, self.vd if self.vd != self.hd else None, self.keep_first, blocks=self.blocks)
@@ -107,6 +122,12 @@ class PagedAttention:
         if self.row_norm is not None:
             out += [ParamSpec(self.row_norm["q"], (self.nq * self.hd_file,), "vector"),
                     ParamSpec(self.row_norm["k"], (self.nkv * self.hd_file,), "vector")]
+        if self.bias_names is not None:
+            out += [ParamSpec(self.bias_names["q"], (self.nq * self.hd_file,), "vector"),
+                    ParamSpec(self.bias_names["k"], (self.nkv * self.hd_file,), "vector"),
+                    ParamSpec(self.bias_names["v"], (self.nkv * self.vd_file,), "vector")]
+        if self.value_mix is not None:
+            out.append(ParamSpec(self.value_mix["weight"], (), "vector"))
         return out
 
     def load(self, fetch):
@@ -129,10 +150,19 @@ class PagedAttention:
             gains = [heads_padded(fetch(self.row_norm[k])[:, None], heads, self.hd_file, self.hd)[:, 0].contiguous()
                      for k, heads in (("q", self.nq), ("k", self.nkv))]
             self.q_gain, self.k_gain = gains
+        if self.bias_names is not None:
+            rows = [heads_padded(fetch(self.bias_names[k]).to(torch.float32)[:, None], heads, size, to)[:, 0]
+                    for k, heads, size, to in (("q", self.nq, self.hd_file, self.hd), ("k", self.nkv, self.hd_file, self.hd),
+                                               ("v", self.nkv, self.vd_file, self.vd))]
+            self.bias = torch.cat(rows).contiguous()
+        if self.value_mix is not None:
+            self.blend = fetch(self.value_mix["weight"]).to(torch.float32).reshape(1).contiguous()
         wo = fetch(n["o_proj"])
         self.wo = heads_padded(wo.t().contiguous(), self.nq, self.vd_file, self.vd).t().contiguous()
         if self.sink_name is not None:
             self.sinks = fetch(self.sink_name).to(torch.float32).contiguous()
+        if self.slope_values is not None:
+            self.slopes = torch.tensor(self.slope_values, dtype=torch.float64).to(torch.float32).to(self.wo.device)
         self.position.to(self.wo.device)
 
     def input_weights(self) -> list:
@@ -164,7 +194,7 @@ class PagedAttention:
             ops.rope_row_norm_kv_write(qkv, q, ctx.positions, slots, self.position.inv_freq, k_pages, v_pages, self.nq, self.nkv,
                                        self.hd, self.position.rotary_dim, group.page_size, self.q_gain, self.k_gain,
                                        float(self.row_norm["eps"]), self.nq * self.hd_file, self.nkv * self.hd_file,
-                                       in_splits=parts, pairing=pairing, vd=self.vd)
+                                       in_splits=parts, pairing=pairing, vd=self.vd, bias=self.bias, **self._blend_args(n, ctx))
         else:
             ops.rope_kv_write(qkv[..., :self.qkv_width] if self.width != self.qkv_width else qkv, q, ctx.positions, slots,
                               self.position.inv_freq, k_pages, v_pages, self.nq, 0 if self.borrows else self.nkv, self.hd,
@@ -174,6 +204,13 @@ class PagedAttention:
         if self.gate_name is not None:
             ops.sigmoid_gate(attn, qkv, parts, self.qkv_width)
         return as_branch(ops.project(attn, self.wo, lambda name, shape, dt: ctx.buffer(self.tag + "branch_" + name, shape, dt)))
+
+    def _blend_args(self, n: int, ctx) -> dict:
+        """The buffer of the step in which the first layer of a label leaves its values, and this layer's part in it."""
+        if self.value_mix is None:
+            return {}
+        first = ctx.buffer("values_first_" + str(self.value_mix["key"]), (n, self.nkv * self.vd), torch.float32)
+        return {"v_first": first, "blend": self.blend, "mix": self.value_mix["role"]}
 
     def attend(self, q, out, k_pages, v_pages, ctx, group: int) -> None:
         """Attention of every token of the step over its request's pages of cache group `group`."""
@@ -185,6 +222,8 @@ class PagedAttention:
             # 32 rows of a request share every tile of keys.  Few rows over long contexts (decoding): a warp per
             # (row, chunk of 64 keys).  Otherwise a warp per row.
             extra = {"vd": self.vd, "sinks": self.sinks} if (self.general or self.sinks is not None) else {}
+            if self.slopes is not None:
+                extra["slopes"] = self.slopes
             if self.softcap > 0 or self.keep_first > 0:
                 extra.update(cap=self.softcap, keep=self.keep_first)
             if ctx.num_multi > 0 and hd <= 256 and self.vd <= 256:

@@ -5,7 +5,12 @@
 A branch's output is left pending on the residual and folded in by the next norm
 (the next block's, or the model's final one).
 
-spec options: norm_in, mixer, norm_post, feed_forward (specs).
+`feed_forward` may be absent: the block then has its first sublayer only.  With `token_input` the block ends with a
+third addend that reads the residual as it then stands (through `reader`, kind 'identity') and the step's token ids, and
+joins the residual through a norm of its own, x = x + token_input_norm(token_input(x, tokens)); it stays pending as a
+`NormedBranch`, so the next norm of the residual runs that norm, the add and itself in one kernel.
+
+spec options: norm_in, mixer, and norm_post, feed_forward (both or none), and token_input, token_input_norm, reader (all three or none).
 
 'sandwich': a norm in front of and behind each sublayer,
     x = x + norm_mixer_out(mixer(norm_in(x)));  x = x + norm_ff_out(feed_forward(norm_post(x)))
@@ -33,18 +38,32 @@ class PreNormBlock:
         kw = dict(hidden_size=hidden_size, model_dtype=model_dtype)
         self.norm_in = NORMS.build(spec.norm_in, **kw)
         self.mixer = MIXERS.build(spec.mixer, **kw)
-        self.norm_post = NORMS.build(spec.norm_post, **kw)
-        self.feed_forward = FEED_FORWARDS.build(spec.feed_forward, **kw)
+        self.feed_forward = self.token_input = None
+        if spec.options.get("feed_forward") is not None:
+            self.norm_post = NORMS.build(spec.norm_post, **kw)
+            self.feed_forward = FEED_FORWARDS.build(spec.feed_forward, **kw)
+        if spec.options.get("token_input") is not None:
+            self.reader = NORMS.build(spec.reader, **kw)
+            self.token_input = FEED_FORWARDS.build(spec.token_input, **kw)
+            self.token_input_norm = NORMS.build(spec.token_input_norm, **kw)
 
     def parts(self):
-        return [self.norm_in, self.mixer, self.norm_post, self.feed_forward]
+        out = [self.norm_in, self.mixer]
+        if self.feed_forward is not None:
+            out += [self.norm_post, self.feed_forward]
+        if self.token_input is not None:
+            out += [self.reader, self.token_input, self.token_input_norm]
+        return out
 
     def cache_need(self):
         return self.mixer.cache_need()
 
     def __call__(self, residual: Residual, ctx, cache: CacheRef) -> None:
         residual.pending = self.mixer(self.norm_in(residual, ctx), ctx, cache)
-        residual.pending = self.feed_forward(self.norm_post(residual, ctx), ctx)
+        if self.feed_forward is not None:
+            residual.pending = self.feed_forward(self.norm_post(residual, ctx), ctx)
+        if self.token_input is not None:
+            residual.pending = NormedBranch(self.token_input(self.reader(residual, ctx), ctx), self.token_input_norm)
 
 
 @BLOCKS.register("sandwich")

@@ -3,7 +3,10 @@
 spec options: num_experts, top, groups, groups_kept (the experts form `groups` equal groups of neighbours; a group's score
 is its best expert's and only experts of the `groups_kept` best groups can be chosen; 1 and 1: no such limit), router
 (checkpoint name of the router matrix [experts, hidden]), expert_prefix (expert j's tensors are <prefix><j>.gate / .up /
-.down), intermediate_size, activation, limit, slope (the experts' gated unit, as 'gated_dense' takes them), shared (None, or
+.down), intermediate_size, activation, limit, slope (the experts' gated unit, as 'gated_dense' takes them), scores ('softmax',
+the default, over all experts; 'sigmoid': expert by expert, not normalised), gated (default True; False: an expert is
+down(act(up x)) with tensors <prefix><j>.up / .down and activation 'relu_squared'), weight_on ('output', the default: the
+chosen experts' outputs are multiplied by their scores; 'input': their inputs are, the output is the sum of expert(s x)), shared (None, or
 the options of a 'gated_dense' unit that every token runs, plus gate_weight: the checkpoint name of one row [1, hidden]; the
 unit's output is multiplied by sigmoid(row . x)).
 
@@ -33,9 +36,16 @@ class RoutedExperts:
         if self.E % self.groups or not 1 <= self.groups_kept <= self.groups or not 1 <= self.top <= self.groups_kept * (self.E // self.groups):
             raise ValueError(f"{self.E} experts in {self.groups} groups, {self.groups_kept} kept, top {self.top}: no such choice")
         self.inter, self.activation = int(spec.intermediate_size), spec.activation
-        if self.activation != "capped_swish":
-            raise ValueError("the grouped expert products are built for the activation capped_swish")
-        self.limit, self.slope = float(spec.limit), float(spec.slope)
+        self.gated = bool(spec.options.get("gated", True))
+        self.scores, self.weight_on = spec.options.get("scores") or "softmax", spec.options.get("weight_on") or "output"
+        if self.scores not in ("softmax", "sigmoid") or self.weight_on not in ("output", "input"):
+            raise ValueError(f"scores {self.scores!r} ('softmax', 'sigmoid'), weight_on {self.weight_on!r} ('output', 'input')")
+        if self.activation != ("capped_swish" if self.gated else "relu_squared"):
+            raise ValueError("the grouped expert products are built for gated experts with the activation capped_swish and for "
+                             "experts without a gate with relu_squared")
+        if self.weight_on == "input" and self.gated:
+            raise ValueError("scores on the experts' inputs are built for experts without a gate")
+        self.limit, self.slope = float(spec.options.get("limit") or 0.0), float(spec.options.get("slope") or 0.0)
         self.router_name, self.prefix = spec.router, spec.expert_prefix
         self.hidden_size, self.model_dtype = hidden_size, model_dtype
         self.shared = self.gate_name = None
@@ -54,7 +64,7 @@ class RoutedExperts:
         out = [ParamSpec(self.router_name, (self.E, H))]
         for j in range(self.E):
             p = f"{self.prefix}{j}."
-            out += [ParamSpec(p + "gate", (I, H)), ParamSpec(p + "up", (I, H)), ParamSpec(p + "down", (H, I))]
+            out += ([ParamSpec(p + "gate", (I, H))] if self.gated else []) + [ParamSpec(p + "up", (I, H)), ParamSpec(p + "down", (H, I))]
         if self.shared is not None:
             out += self.shared.param_specs() + [ParamSpec(self.gate_name, (1, H))]
         return out
@@ -62,7 +72,10 @@ class RoutedExperts:
     def load(self, fetch):
         self.w_router = fetch(self.router_name).to(torch.float32).contiguous()
         names = [f"{self.prefix}{j}." for j in range(self.E)]
-        self.w_gu = torch.stack([torch.cat([fetch(p + "gate"), fetch(p + "up")], dim=0) for p in names]).contiguous()
+        if self.gated:
+            self.w_gu = torch.stack([torch.cat([fetch(p + "gate"), fetch(p + "up")], dim=0) for p in names]).contiguous()
+        else:
+            self.w_gu = torch.stack([fetch(p + "up") for p in names]).contiguous()
         self.w_down = torch.stack([fetch(p + "down") for p in names]).contiguous()
         if self.shared is not None:
             self.shared.load(fetch)
@@ -74,7 +87,9 @@ class RoutedExperts:
         chosen = ctx.buffer("moe_chosen", (n, top), torch.int32)
         weights = ctx.buffer("moe_weights", (n, top), torch.float32)
         gate = ctx.buffer("moe_gate", (n,), torch.float32) if self.shared is not None else None
-        ops.moe_route(x, self.w_router, self.w_gate, chosen, weights, gate, self.groups, self.groups_kept)
+        ops.moe_route(x, self.w_router, self.w_gate, chosen, weights, gate, self.groups, self.groups_kept, scores=self.scores)
+        unit = None if self.gated else self.activation
+        on_input = weights.view(-1) if self.weight_on == "input" else None
         index = ctx.buffer("moe_index", (2 * self.E + 1 + 2 * pairs,), torch.int32)
         count, offset = index[:self.E], index[self.E:2 * self.E + 1]
         order, place = index[2 * self.E + 1:2 * self.E + 1 + pairs], index[2 * self.E + 1 + pairs:]
@@ -86,13 +101,15 @@ class RoutedExperts:
         if pairs >= self.TC_FROM_PAIRS and x.dtype == torch.bfloat16 and ops.tc_grouped_ok(x, self.w_gu) and self.inter % 8 == 0:
             tiles = ctx.buffer("moe_tiles", (1 + 3 * ops.moe_row_tiles(pairs, self.E),), torch.int32)
             ops.moe_plan(chosen, count, offset, order, place, tiles, ctx.buffer("moe_plan", (ops.MOE_PLAN_SEGMENTS * self.E,), torch.int32))
-            rows = ops.moe_gather(x, order, top, ctx.buffer("moe_rows", (pairs, H), self.model_dtype))
-            ops.gemm_bf16_tc_grouped(rows, self.w_gu, act, tiles, True, self.limit, self.slope)
+            # (scores on the inputs: the rows are multiplied while they are copied, rounded once)
+            rows = ops.moe_gather(x, order, top, ctx.buffer("moe_rows", (pairs, H), self.model_dtype), row_weights=on_input)
+            ops.gemm_bf16_tc_grouped(rows, self.w_gu, act, tiles, self.gated, self.limit, self.slope, unit=unit)
             ops.gemm_bf16_tc_grouped(act, self.w_down, y, tiles, False)
         else:
             ops.moe_plan(chosen, count, offset, order, place)
-            ops.moe_grouped(x, self.w_gu, act, offset, order, top, True, self.limit, self.slope)
+            # (scores on the inputs: the up product is linear, so the score multiplies its 32-bit sums in front of the activation)
+            ops.moe_grouped(x, self.w_gu, act, offset, order, top, self.gated, self.limit, self.slope, unit=unit, row_weights=on_input)
             ops.moe_grouped(act, self.w_down, y, offset, order, top, False)
         shared = branch_pair(self.shared(x, ctx)) if self.shared is not None else None
         out = ctx.buffer("moe_out", (n, H), torch.float32)
-        return ops.moe_combine(y, place, weights, shared, gate, out)
+        return ops.moe_combine(y, place, None if self.weight_on == "input" else weights, shared, gate, out)

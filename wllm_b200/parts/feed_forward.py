@@ -11,6 +11,12 @@ epilogue, in 32-bit on the accumulators; otherwise one product feeds the activat
 
 Kind 'dense' (no gate).  spec options: intermediate_size, activation ('relu_squared': max(z, 0)^2), up_proj/down_proj
 (checkpoint names).  Under bfloat16 the activation is the epilogue of the up product, on the 32-bit accumulators.
+
+Kind 'token_gated_table': a per-token addend made from the token itself.  A table holds a row per token id; the part reads
+`dim` columns of it from `first_column` on (several layers share one table, each with columns of its own) and computes
+out_proj(act(gate_proj x) * row).  spec options: table (checkpoint name), vocab_size, table_width (columns of the whole
+table), first_column, dim, activation ('gelu_tanh'), gate_proj [dim, hidden], out_proj [hidden, dim] (checkpoint names).
+It reads the step's token ids from the step context.  Only the part's own columns of the table are kept on the device.
 """
 from __future__ import annotations
 
@@ -79,3 +85,36 @@ class Dense:
         h = ops.unit_linear(x, self.wu, self.activation, ctx.buffer("ffn_act", (n, self.inter), self.model_dtype),
                             lambda shape, dtype: ctx.buffer("ffn_up", shape, dtype))
         return as_branch(ops.project(h, self.wd, lambda name, shape, dt: ctx.buffer("branch_" + name, shape, dt)))
+
+
+@FEED_FORWARDS.register("token_gated_table")
+class TokenGatedTable:
+    graph_safe = True
+
+    def __init__(self, spec, hidden_size: int, model_dtype: torch.dtype):
+        self.vocab, self.table_width = int(spec.vocab_size), int(spec.table_width)
+        self.first, self.dim = int(spec.first_column), int(spec.dim)
+        if self.first < 0 or self.first + self.dim > self.table_width:
+            raise ValueError(f"columns {self.first} .. {self.first + self.dim} lie outside a table of {self.table_width} columns")
+        self.activation = spec.activation
+        if self.activation not in ops.TOKEN_GATE_ACTIVATIONS:
+            raise ValueError(f"activation {self.activation!r}: one of {', '.join(ops.TOKEN_GATE_ACTIVATIONS)}")
+        self.hidden_size, self.model_dtype = hidden_size, model_dtype
+        self.names = {k: spec.options[k] for k in ("table", "gate_proj", "out_proj")}
+        self.table = self.w_gate = self.w_out = None
+
+    def param_specs(self):
+        H, n = self.hidden_size, self.names
+        return [ParamSpec(n["table"], (self.vocab, self.table_width), "table"), ParamSpec(n["gate_proj"], (self.dim, H)),
+                ParamSpec(n["out_proj"], (H, self.dim))]
+
+    def load(self, fetch):
+        self.table = fetch(self.names["table"])[:, self.first:self.first + self.dim].contiguous()
+        self.w_gate = fetch(self.names["gate_proj"]).contiguous()
+        self.w_out = fetch(self.names["out_proj"]).contiguous()
+
+    def __call__(self, x: torch.Tensor, ctx):
+        n = x.shape[0]
+        z, parts = ops.project(x, self.w_gate, lambda name, shape, dt: ctx.buffer("token_gate_" + name, shape, dt))
+        g = ops.token_gate(z, parts, ctx.token_ids, self.table, self.activation, ctx.buffer("token_gated", (n, self.dim), self.model_dtype))
+        return as_branch(ops.project(g, self.w_out, lambda name, shape, dt: ctx.buffer("token_branch_" + name, shape, dt)))

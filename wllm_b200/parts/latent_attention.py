@@ -6,6 +6,11 @@ itself and the window - 1 keys before it), eps (of the latent row's norm), posit
 q_proj [heads * (plain_dim + rot_dim), hidden], down_proj [kv_rank + rot_dim, hidden], latent_norm [kv_rank],
 up_k [heads * plain_dim, kv_rank], up_v [heads * value_dim, kv_rank], o_proj [hidden, heads * value_dim] (checkpoint names).
 
+Two more options.  query_latent ({"rank": r, "down": name [r, hidden], "norm": name [r], "up": name [heads * plain_dim, r]};
+without a turning part): the queries are up(rms(down h) * gain) instead of q_proj h, with the eps of the latent row's norm.
+gate_proj (name of a matrix [heads * value_dim, hidden]): the heads' outputs are multiplied by the sigmoid of that
+projection of the mixer's input before the output projection.  Both ride on the one fused product of the mixer's input.
+
 With h the mixer's input: q = q_proj h, head by head [plain | turning]; the down projection gives the latent row
 c = rms(first kv_rank rows) * gain and, behind it, one turning key part t shared by all heads.  Head a's key is
 [up_k_a c | turned t], its value up_v_a c, its score scale * (q_a . k_a), softmax over the visible keys.
@@ -42,25 +47,48 @@ class LatentAttention:
             raise ValueError(f"the rotary encoding covers {self.position.head_dim} elements, the turning part has {self.rot}")
         # a cached row is held in steps of 8 elements (16-byte loads), zeros behind the turned part
         self.row = -(-(self.rank + self.rot) // 8) * 8
-        self.names = {k: spec.options[k] for k in ("q_proj", "down_proj", "latent_norm", "up_k", "up_v", "o_proj")}
-        self.q_width = self.heads * (self.dim + self.rot)
-        self.width = self.q_width + self.rank + self.rot            # columns of the fused product
+        self.qlat = spec.options.get("query_latent")
+        self.gate_name = spec.options.get("gate_proj")
+        self.names = {k: spec.options[k] for k in ("down_proj", "latent_norm", "up_k", "up_v", "o_proj")}
+        if self.qlat is None:
+            self.names["q_proj"] = spec.options["q_proj"]
+            self.q_rank = 0
+        else:
+            if self.rot:
+                raise ValueError("queries through a latent row of their own have no turning part")
+            self.q_rank = int(self.qlat["rank"])
+        self.q_width = self.q_rank if self.q_rank else self.heads * (self.dim + self.rot)
+        self.gate_col = self.q_width + self.rank + self.rot
+        self.width = self.gate_col + (self.heads * self.vd if self.gate_name is not None else 0)    # columns of the fused product
         self.tag = ""
-        self.w_in = self.w_uk_t = self.w_uv = self.wo = self.gain = None
+        self.w_in = self.w_uk_t = self.w_uv = self.wo = self.gain = self.q_gain = self.w_uq = None
 
     def cache_need(self):
         return KVNeed(1, self.row, self.window, self.rank, 0, values_in_keys=True)
 
     def param_specs(self):
         H, n = self.hidden_size, self.names
-        return [ParamSpec(n["q_proj"], (self.q_width, H)), ParamSpec(n["down_proj"], (self.rank + self.rot, H)),
-                ParamSpec(n["latent_norm"], (self.rank,), "vector"), ParamSpec(n["up_k"], (self.heads * self.dim, self.rank)),
-                ParamSpec(n["up_v"], (self.heads * self.vd, self.rank)), ParamSpec(n["o_proj"], (H, self.heads * self.vd))]
+        if self.qlat is None:
+            out = [ParamSpec(n["q_proj"], (self.q_width, H))]
+        else:
+            out = [ParamSpec(self.qlat["down"], (self.q_rank, H)), ParamSpec(self.qlat["norm"], (self.q_rank,), "vector"),
+                   ParamSpec(self.qlat["up"], (self.heads * self.dim, self.q_rank))]
+        if self.gate_name is not None:
+            out.append(ParamSpec(self.gate_name, (self.heads * self.vd, H)))
+        return out + [ParamSpec(n["down_proj"], (self.rank + self.rot, H)),
+                      ParamSpec(n["latent_norm"], (self.rank,), "vector"), ParamSpec(n["up_k"], (self.heads * self.dim, self.rank)),
+                      ParamSpec(n["up_v"], (self.heads * self.vd, self.rank)), ParamSpec(n["o_proj"], (H, self.heads * self.vd))]
 
     def load(self, fetch):
         n = self.names
-        self.w_in = torch.cat([fetch(n["q_proj"]), fetch(n["down_proj"])], dim=0).contiguous()
+        mats = [fetch(n["q_proj"] if self.qlat is None else self.qlat["down"]), fetch(n["down_proj"])]
+        if self.gate_name is not None:
+            mats.append(fetch(self.gate_name))
+        self.w_in = torch.cat(mats, dim=0).contiguous()
         self.gain = fetch(n["latent_norm"]).contiguous()
+        if self.qlat is not None:
+            self.q_gain = fetch(self.qlat["norm"]).to(self.gain.dtype).contiguous()
+            self.w_uq = fetch(self.qlat["up"]).contiguous()
         # up_k head by head, transposed: [heads, kv_rank, plain_dim], so that the queries' map is x W^T like every product
         self.w_uk_t = fetch(n["up_k"]).view(self.heads, self.dim, self.rank).transpose(1, 2).contiguous()
         self.w_uv = fetch(n["up_v"]).view(self.heads, self.vd, self.rank).contiguous()
@@ -83,17 +111,24 @@ class LatentAttention:
         pages = group.keys(cache.layer)
         # a product that left one tensor in the model's type holds the queries' plain parts as the next product reads them
         in_place = parts == 0 and cols.dtype == self.model_dtype
-        q_plain = None if in_place else ctx.buffer(self.tag + "latent_q_plain", (n, H * self.dim), self.model_dtype)
+        q_plain = None if in_place or self.q_rank else ctx.buffer(self.tag + "latent_q_plain", (n, H * self.dim), self.model_dtype)
         q_mapped = ctx.buffer(self.tag + "latent_q", (n, H * row), self.model_dtype)
+        cq = ctx.buffer(self.tag + "latent_cq", (n, self.q_rank), self.model_dtype) if self.q_rank else None
         ops.latent_prepare(cols, parts, ctx.positions, ctx.group_slots[cache.group], self.position.inv_freq, self.gain, self.eps,
                            pages, group.page_size, q_plain, q_mapped, H, self.dim, self.rot, self.position.rotary_dim, R, row,
-                           pairing=getattr(self.position, "pairing", "half"))
-        plain = cols[:, :self.q_width].unflatten(1, (H, self.dim + self.rot))[:, :, :self.dim] if in_place else q_plain.view(n, H, self.dim)
+                           pairing=getattr(self.position, "pairing", "half"), q_rank=self.q_rank, q_gain=self.q_gain, cq_out=cq)
+        if self.q_rank:
+            # the queries from their normed latent row: one more product, then head by head as below
+            plain = ops.linear(cq, self.w_uq, ctx.buffer(self.tag + "latent_q_up", (n, H * self.dim), self.model_dtype)).view(n, H, self.dim)
+        else:
+            plain = cols[:, :self.q_width].unflatten(1, (H, self.dim + self.rot))[:, :, :self.dim] if in_place else q_plain.view(n, H, self.dim)
         ops.head_linear(plain, self.w_uk_t, q_mapped.view(n, H, row)[:, :, :R])
         mixed = ctx.buffer(self.tag + "latent_mixed", (n, H * R), self.model_dtype)
         self.attend(q_mapped, mixed, pages, ctx, cache.group)
         heads_out = ctx.buffer(self.tag + "attn", (n, H * self.vd), self.model_dtype)
         ops.head_linear(mixed.view(n, H, R), self.w_uv, heads_out.view(n, H, self.vd))
+        if self.gate_name is not None:
+            ops.sigmoid_gate(heads_out, cols, parts, self.gate_col)
         return as_branch(ops.project(heads_out, self.wo, lambda name, shape, dt: ctx.buffer(self.tag + "branch_" + name, shape, dt)))
 
     def attend(self, q, out, pages, ctx, group: int) -> None:

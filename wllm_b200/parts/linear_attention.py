@@ -19,6 +19,21 @@ the projections run in the model's element type.
 'parallel_mean': two mixers read the same input; each output is root-mean-square normed over the model width with a
 gain of its own, and the result is half their sum.  One product serves both (`input_weights` / `mix`).
 spec options: left, right (mixer specs), left_out, right_out (names of the gains), eps.
+'delta_rule': the gated delta rule.  Per head a state S [dim, vdim] in the request's state slot, 32-bit; every token first
+decays it, then corrects it towards its value along its key, then reads it with its query:
+
+    S <- g_t S;    u_t = beta_t (v_t - S^T k_t);    S <- S + k_t u_t^T;    o_t = S^T q_t
+
+q, k (num_kv_heads heads of key_dim; value head h reads q/k head h // (num_heads / num_kv_heads)) and v (num_heads heads of
+value_dim) pass a short causal convolution over time per channel (`conv_taps` taps, the last one the token's own, zeros before
+the sequence's start; its last taps - 1 inputs are state too) and SiLU; q and k heads are divided by sqrt(sum(x^2) +
+unit_norm_eps), q is also multiplied by q_scale; beta_t = sigmoid(beta_proj x) and g_t = exp(-exp(decay_log) softplus(decay_proj x +
+decay_bias)), one of each per head.  Each head's o is divided by its root mean square over value_dim (eps), times the gain
+head_norm_weight shared by the heads, times silu(g_proj x); then o_proj.
+spec options: num_heads, num_kv_heads, key_dim, value_dim, conv_taps, eps, unit_norm_eps, q_scale, q_proj/k_proj/v_proj/g_proj/
+o_proj, q_conv/k_conv/v_conv [channels, taps], beta_proj, decay_proj [heads, hidden], decay_log, decay_bias [heads],
+head_norm_weight [value_dim] (checkpoint names).  One product makes q | k | v | g | beta | decay; what enters the
+recurrence is 32-bit (csrc/delta_rule.cu).
 """
 from __future__ import annotations
 
@@ -196,3 +211,81 @@ class ParallelMean:
         b = self.right.mix(fused, parts, self.left_width, ctx, self._side(cache, "right"))
         # half the sum of the two normed outputs is taken by whoever reads the branch (the next norm's kernel)
         return MeanOfNormed(a, self.gain_left, b, self.gain_right, self.eps, 0.5)
+
+
+@MIXERS.register("delta_rule")
+class DeltaRule:
+    graph_safe = True
+
+    def __init__(self, spec, hidden_size: int, model_dtype: torch.dtype):
+        self.heads, self.kv_heads = int(spec.num_heads), int(spec.num_kv_heads)
+        self.dim, self.vdim, self.taps = int(spec.key_dim), int(spec.value_dim), int(spec.conv_taps)
+        if self.heads % self.kv_heads:
+            raise ValueError(f"{self.heads} heads are no multiple of {self.kv_heads} query/key heads")
+        if self.dim > 256 or self.vdim > 256 or not 1 <= self.taps <= 16:
+            raise ValueError(f"key_dim {self.dim}, value_dim {self.vdim}, conv_taps {self.taps}: the kernels hold heads of up to 256 "
+                             f"channels and convolutions of up to 16 taps")
+        self.eps, self.unit_eps, self.q_scale = float(spec.eps), float(spec.unit_norm_eps), float(spec.options.get("q_scale", 1.0))
+        self.hidden_size, self.model_dtype = hidden_size, model_dtype
+        self.names = {k: spec.options[k] for k in ("q_proj", "k_proj", "v_proj", "g_proj", "o_proj", "q_conv", "k_conv", "v_conv",
+                                                   "beta_proj", "decay_proj", "decay_log", "decay_bias", "head_norm_weight")}
+        GD, HV = self.kv_heads * self.dim, self.heads * self.vdim
+        self.offsets = {"q": 0, "k": GD, "v": 2 * GD, "g": 2 * GD + HV, "b": 2 * GD + 2 * HV, "a": 2 * GD + 2 * HV + self.heads}
+        self.width = 2 * GD + 2 * HV + 2 * self.heads
+        self.channels = 2 * GD + HV
+        self.tag = ""
+        self.w_in = self.wo = self.conv = self.a_log = self.dt_bias = self.norm_weight = None
+
+    def cache_need(self):
+        need = [("state", (self.heads, self.dim, self.vdim), torch.float32)]
+        if self.taps > 1:
+            need.append(("conv", (self.taps - 1, self.channels), torch.float32))
+        return StateNeed(tuple(need))
+
+    def param_specs(self):
+        H, n, GD, HV = self.hidden_size, self.names, self.kv_heads * self.dim, self.heads * self.vdim
+        return [ParamSpec(n["q_proj"], (GD, H)), ParamSpec(n["k_proj"], (GD, H)), ParamSpec(n["v_proj"], (HV, H)),
+                ParamSpec(n["g_proj"], (HV, H)), ParamSpec(n["beta_proj"], (self.heads, H)), ParamSpec(n["decay_proj"], (self.heads, H)),
+                ParamSpec(n["o_proj"], (H, HV)), ParamSpec(n["q_conv"], (GD, self.taps)), ParamSpec(n["k_conv"], (GD, self.taps)),
+                ParamSpec(n["v_conv"], (HV, self.taps)), ParamSpec(n["decay_log"], (self.heads,), "vector"),
+                ParamSpec(n["decay_bias"], (self.heads,), "vector"), ParamSpec(n["head_norm_weight"], (self.vdim,), "vector")]
+
+    def load(self, fetch):
+        n = self.names
+        mats = [fetch(n[k]) for k in ("q_proj", "k_proj", "v_proj", "g_proj", "beta_proj", "decay_proj")]
+        pad = -self.width % 8             # the product's rows in steps of 8 columns (16 bytes of the matrix type)
+        if pad:
+            mats.append(mats[0].new_zeros((pad, self.hidden_size)))
+        self.w_in = torch.cat(mats, dim=0).contiguous()
+        self.wo = fetch(n["o_proj"]).contiguous()
+        self.conv = [fetch(n[k]).contiguous() for k in ("q_conv", "k_conv", "v_conv")]
+        self.a_log = fetch(n["decay_log"]).to(self.conv[0].dtype).contiguous()
+        self.dt_bias = fetch(n["decay_bias"]).to(self.conv[0].dtype).contiguous()
+        self.norm_weight = fetch(n["head_norm_weight"]).contiguous()
+
+    def input_weights(self) -> list:
+        return [self.w_in]
+
+    def __call__(self, x: torch.Tensor, ctx, cache: CacheRef):
+        fused, parts = ops.project(x, self.w_in, lambda name, shape, dt: ctx.buffer(self.tag + "delta_in_" + name, shape, dt))
+        return self.mix(fused, parts, 0, ctx, cache)
+
+    def mix(self, fused: torch.Tensor, parts: int, col0: int, ctx, cache: CacheRef):
+        """The mixer on the columns from col0 of a fused product [n, W] (or partial sums [parts, n, W])."""
+        n, H, G, D, V, f32 = fused.shape[-2], self.heads, self.kv_heads, self.dim, self.vdim, torch.float32
+        off = {k: col0 + v for k, v in self.offsets.items()}
+        q = ctx.buffer(self.tag + "delta_q", (n, G * D), f32)
+        k = ctx.buffer(self.tag + "delta_k", (n, G * D), f32)
+        v = ctx.buffer(self.tag + "delta_v", (n, H * V), f32)
+        beta = ctx.buffer(self.tag + "delta_beta", (n, H), f32)
+        decay = ctx.buffer(self.tag + "delta_decay", (n, H), f32)
+        conv_state = ctx.state(cache.state_names["conv"]) if self.taps > 1 else None
+        ops.delta_prepare(fused, parts, off, H, G, D, V, self.taps, *self.conv, self.a_log, self.dt_bias, ctx.token_req,
+                          ctx.req_q_start, ctx.req_slot, conv_state, self.unit_eps, self.q_scale, q, k, v, beta, decay)
+        ops.delta_conv_update(fused, parts, off, H, G, D, V, self.taps, ctx.req_q_start, ctx.req_q_len, ctx.req_slot, conv_state)
+        o = ctx.buffer(self.tag + "delta_o", (n, H * V), f32)
+        ops.delta_scan(q, k, v, beta, decay, ctx.state(cache.state_names["state"]), o, ctx.req_q_start, ctx.req_q_len, ctx.req_slot,
+                       H, G, D, V)
+        gated = ctx.buffer(self.tag + "delta_gated", (n, H * V), self.model_dtype)
+        ops.head_gate_norm(o, fused, parts, off["g"], self.norm_weight, self.eps, gated, H, V)
+        return as_branch(ops.project(gated, self.wo, lambda name, shape, dt: ctx.buffer(self.tag + "delta_out_" + name, shape, dt)))

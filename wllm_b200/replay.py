@@ -13,7 +13,8 @@ logits are wanted); `end` lists the requests that are finished after the step, w
 pages go back to the pool.  For a step that wants something, `<out>/<step>.f32`
 receives the logits [wanted, vocab] as little-endian 32-bit floats in the order of
 the entries and of `want`.  After every step a line `done <step>` is printed and
-flushed.  The pool holds ceil(N / page size) pages, so pages are used again.
+flushed.  The pool holds ceil(N / page size) pages and `--max-requests` state slots (4 unless told otherwise), so pages and
+slots are used again.
 """
 from __future__ import annotations
 
@@ -31,6 +32,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
     ap.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
+    ap.add_argument("--max-requests", type=int, default=4, help="requests that may be live at once (state slots)")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 
@@ -38,7 +40,7 @@ def main(argv=None) -> int:
     from .engine import StepEntry, build_model, build_runner
 
     os.makedirs(args.out, exist_ok=True)
-    engine = EngineConfig(dtype=args.dtype, block_size=args.block_size, max_num_seqs=16, device=args.device)
+    engine = EngineConfig(dtype=args.dtype, block_size=args.block_size, max_num_seqs=args.max_requests, device=args.device)
     model = build_model(args.model, engine.dtype, engine.device)
     pages = max(1, -(-args.max_tokens // engine.block_size))
     runner = build_runner(model, engine, num_pages=pages)
