@@ -49,7 +49,7 @@ def silu(z):
 
 def embed(cfg, w, tokens):
     n = len(tokens)
-    return w["embed"][tokens] * float(cfg["embedding"]["scale"]) + w["pos"][:n]
+    return w["embed"][tokens] * float((cfg.get("embedding") or {}).get("scale", 1.0)) + w["pos"][:n]
 
 
 def softmax_rows(scores, visible):
@@ -70,7 +70,8 @@ def window_visible(n, size):
 
 def attention(m, w, p, h, eps, v_first):
     """Returns (output, the layer's own values before mixing)."""
-    n, H, G, D, V = h.shape[0], m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    n, H, D = h.shape[0], m["heads"], m["dim"]
+    G, V, scale = m.get("kv_heads", H), m.get("vdim", D), float(m.get("scale", D ** -0.5))
     q = h @ w[p + "q"].T + w[p + "q.b"]
     k = h @ w[p + "k"].T + w[p + "k.b"]
     v = h @ w[p + "v"].T + w[p + "v.b"]
@@ -88,7 +89,7 @@ def attention(m, w, p, h, eps, v_first):
     out = []
     for a in range(H):
         g = a // (H // G)
-        s = (q[:, a] @ k[:, g].T) * float(m["scale"]) - sl[a] * dist
+        s = (q[:, a] @ k[:, g].T) * scale - sl[a] * dist
         out.append(softmax_rows(s, visible) @ v[:, g])
     return torch.cat(out, dim=-1) @ w[p + "o"].T, own
 
@@ -103,7 +104,7 @@ def latent_attention(m, w, p, h, eps):
     visible = window_visible(n, None)
     out = []
     for a in range(H):
-        s = (q[:, a] @ k[:, a].T) * float(m["scale"])
+        s = (q[:, a] @ k[:, a].T) * float(m.get("scale", D ** -0.5))
         out.append(softmax_rows(s, visible) @ v[:, a])
     heads = torch.cat(out, dim=-1) * torch.sigmoid(h @ w[p + "g"].T)
     return heads @ w[p + "o"].T
@@ -124,7 +125,8 @@ def unit(x):
 
 
 def delta(m, w, p, h, eps):
-    n, H, G, D, V = h.shape[0], m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    n, H, D, V = h.shape[0], m["heads"], m["dim"], m["vdim"]
+    G = m.get("kv_heads", H)
     q = silu(short_conv(h @ w[p + "q"].T, w[p + "q.conv"])).view(n, G, D)
     k = silu(short_conv(h @ w[p + "k"].T, w[p + "k.conv"])).view(n, G, D)
     v = silu(short_conv(h @ w[p + "v"].T, w[p + "v.conv"])).view(n, H, V)
