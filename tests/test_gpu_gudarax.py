@@ -336,6 +336,51 @@ def test_attention_with_a_bias_by_distance_at_every_edge_of_its_window(window, d
     assert window == 1 or (flat - base).abs().max() > 1e-3
 
 
+@pytest.mark.parametrize("hd,n0", [(32, 236), (64, 236), (64, 100), (128, 150)])
+@pytest.mark.parametrize("window", [40, 17, 130, 0])
+def test_tensor_core_attention_with_a_bias_by_distance(window, hd, n0):
+    """The bfloat16 kernels on mma.sync with slopes: a prompt's portion over several tiles of rows and decoded rows of three
+    requests whose keys are cut into splits, one key standing out at every edge of the window, pages of 16 and 64 in
+    scrambled order; grouped heads, so that a tile's rows carry different slopes."""
+    from wllm_b200.kernels import ops
+    g = torch.Generator().manual_seed(window * 7 + hd)
+    H, G, L, dtype = 4, 2, 300, torch.bfloat16
+    scale = 0.4 * (16 / hd) ** 0.5
+    slopes = [2.0 ** (-8.0 * (h + 1) / H) for h in range(H)]
+    sl = torch.tensor(slopes, dtype=torch.float32, device=DEV)
+    k, v = torch.randn(L, G, hd, generator=g).to(dtype), torch.randn(L, G, hd, generator=g).to(dtype)
+    positions = list(range(n0, L))
+    q = torch.randn(len(positions), H, hd, generator=g).to(dtype)
+    one = lambda x: torch.tensor([x], dtype=torch.int32, device=DEV)
+    first = (lambda p: max(0, p - window + 1)) if window else (lambda p: 0)
+    edges = sorted({e for e in (0, first(n0) - 1, first(n0), first(L - 1) - 1, first(L - 1), L - 1, 63, 64, 127, 128) if 0 <= e < L})
+    for ps in (16, 64):
+        for edge in edges:
+            k2 = k.clone()
+            k2[edge] = (q[-1, 0] * 6).to(dtype)[None].expand(G, hd)
+            kp, vp, table = paged(k2, v, ps, 5 + ps)
+            want = plain_window_rows(q, k2, v, positions, scale, window, slopes)
+            qd = q.reshape(len(positions), H * hd).to(DEV)
+            out = torch.empty(len(positions), H * hd, dtype=dtype, device=DEV)
+            ops.attention_mma_prefill(qd, out, kp, vp, one(0), one(len(positions)), one(L), table, len(positions), H, G, hd, ps, window,
+                                      scale, skip_single=False, slopes=sl)
+            err = (out.cpu().double() - want).abs().max()
+            assert err < 0.03, ("prefill", ps, edge, float(err))
+            R = 3
+            tables = table.expand(R, -1).contiguous()
+            starts = torch.arange(R, dtype=torch.int32, device=DEV)
+            lens = torch.ones(R, dtype=torch.int32, device=DEV)
+            ctxs = torch.tensor([L - 2, L - 1, L], dtype=torch.int32, device=DEV)
+            for split_keys, max_splits in ((512, 1), (128, 3), (64, 5)):
+                scratch = torch.empty(ops.attention_mma_scratch_floats(R, H, hd, max_splits), device=DEV)
+                od = torch.empty(R, H * hd, dtype=dtype, device=DEV)
+                ops.attention_mma_decode(qd[-3:].contiguous(), od, kp, vp, starts, lens, ctxs, tables, H, G, hd, ps, window, scale,
+                                         split_keys, max_splits, scratch, slopes=sl)
+                err = (od.cpu().double() - want[-3:]).abs().max()
+                assert err < 0.03, ("decode", ps, edge, split_keys, float(err))
+    assert ops.tc_gemm_status(DEV) == 0
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("sizes", [(4, 2, 16, 24), (5, 1, 10, 6), (2, 2, 64, 64)])
 def test_biases_row_norms_and_blended_values_on_their_way_into_the_pages(sizes, dtype):

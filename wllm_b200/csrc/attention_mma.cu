@@ -179,10 +179,13 @@ struct RowState {
 // thread's two rows may see; `key_base` is the absolute index of tile row 0.
 // `kept_r[i]` / `kept_lo`: keys kept_lo <= key < kept_r[i] are seen as well although they lie before first_r[i] (a sequence's
 // first keys that stay visible behind a window); `capl` > 0: scores (log2 units) become capl * tanh(score / capl).
+// `slope_r[i]` != 0 (log2 units): the score of a key loses slope_r[i] * (at_r[i] - key), at_r[i] being the row's own position
+// (pos_r may be clamped to a split's last key): a bias by distance, after the scale and the cap.
 template <int NKEYS, int QROWS, int KROWS = BN>
 __device__ __forceinline__ void warp_tile(RowState& st, uint32_t q_tile, int q_row0, uint32_t k_tile, uint32_t v_tile, int key0,
                                           int key_base, const int (&pos_r)[2], const int (&first_r)[2], float scale2,
-                                          const int (&kept_r)[2], int kept_lo, float capl) {
+                                          const int (&kept_r)[2], int kept_lo, float capl, const float (&slope_r)[2],
+                                          const int (&at_r)[2]) {
     constexpr int NT = NKEYS / 8;
     const int lane = threadIdx.x & 31;
     const float two_over_cap = capl > 0.f ? 2.0f / capl : 0.f;
@@ -215,6 +218,7 @@ __device__ __forceinline__ void warp_tile(RowState& st, uint32_t q_tile, int q_r
             float v = s[n][c] * scale2;
             // tanh(x) = 1 - 2 / (1 + e^(2x)): two fast operations a score, exact at both ends, 1e-7 absolute near 0
             if (capl > 0.f) v = capl * (1.0f - __fdividef(2.0f, 1.0f + __expf(v * two_over_cap)));
+            if (slope_r[i] != 0.f) v = fmaf(-slope_r[i], (float)(at_r[i] - key), v);
             s[n][c] = ok ? v : -INFINITY;
             mx[i] = fmaxf(mx[i], s[n][c]);
         }
@@ -264,7 +268,8 @@ template <int NKEYS, int QROWS, int KROWS = BN>
 __device__ __forceinline__ void warp_tile(RowState& st, uint32_t q_tile, int q_row0, uint32_t k_tile, uint32_t v_tile, int key0,
                                           int key_base, const int (&pos_r)[2], const int (&first_r)[2], float scale2) {
     const int none[2] = {0, 0};
-    warp_tile<NKEYS, QROWS, KROWS>(st, q_tile, q_row0, k_tile, v_tile, key0, key_base, pos_r, first_r, scale2, none, 0, 0.f);
+    const float flat[2] = {0.f, 0.f};
+    warp_tile<NKEYS, QROWS, KROWS>(st, q_tile, q_row0, k_tile, v_tile, key0, key_base, pos_r, first_r, scale2, none, 0, 0.f, flat, none);
 }
 
 __device__ __forceinline__ void init_state(RowState& st) {
@@ -396,7 +401,7 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
               const int* __restrict__ req_q_start, const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_len,
               const int* __restrict__ block_table, int max_pages, int nq, int nkv, int page_size, int window, float scale2,
               int split_keys, int max_splits, float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ status,
-              const float* __restrict__ sinks, float capl, int keep) {
+              const float* __restrict__ sinks, float capl, int keep, const float* __restrict__ slopes) {
     extern __shared__ unsigned char smem_raw[];
     pdl_begin();
     const int split = blockIdx.z, g = blockIdx.y, r = blockIdx.x;     // CTAs start request by request, the last (shortest) splits last
@@ -436,13 +441,23 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
     const int first_r[2] = {key_lo, key_lo};
     const int hi_r[2] = {min(pos, key_hi - 1), min(pos, key_hi - 1)};
     const int kept_r[2] = {ring.kept_hi, ring.kept_hi};
+    // the tile's rows are the group's query heads: rows lane / 4 and lane / 4 + 8
+    float slope_r[2] = {0.f, 0.f};
+    if (slopes != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int m = (lane >> 2) + 8 * i;
+            slope_r[i] = m < rep ? slopes[g * rep + m] * LOG2E : 0.f;
+        }
+    }
+    const int at_r[2] = {pos, pos};
     int t = 0;                  // place in the ring's walk
     bool ok = true;
     for (; t < ring.count(); ++t) {
         if (!ring.arrive(t)) { ok = false; break; }
         const int s = t % DEC_STAGES;
         warp_tile<16, 16>(st, q_s, 0, ring.k_stage(s), ring.v_stage(s), warp * 16, ring.tile_of(t) * BN, hi_r, first_r, scale2,
-                          kept_r, ring.kept_lo, capl);
+                          kept_r, ring.kept_lo, capl, slope_r, at_r);
     }
     ring.drain(ok ? -1 : t);
     if (!ok) {
@@ -768,7 +783,8 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                const int* __restrict__ req_q_start, const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_len,
                const int* __restrict__ block_table, int max_pages, int nq, int nkv, int page_size, int window, float scale2,
-               int skip_single, int* __restrict__ status, const float* __restrict__ sinks, float capl, int keep) {
+               int skip_single, int* __restrict__ status, const float* __restrict__ sinks, float capl, int keep,
+               const float* __restrict__ slopes) {
     extern __shared__ unsigned char smem_raw[];
     pdl_begin();
     const int g = blockIdx.x, r = blockIdx.y;                 // grid (key/value heads, requests, tiles): the longest tiles start first
@@ -793,9 +809,11 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
     if (keep > 0) { if (key_lo <= keep) key_lo = 0; else kept_cta = keep; }
 
     int pos_r[2], first_r[2], kept_r[2];
+    float slope_r[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const int m = row0 + warp * 16 + (lane >> 2) + i * 8;
+        slope_r[i] = slopes != nullptr ? slopes[g * rep + m % rep] * LOG2E : 0.f;
         pos_r[i] = m < rows ? pos0 + m / rep : -1;                      // a row past the end sees no key
         first_r[i] = first_visible_key(pos_r[i], window);
         kept_r[i] = 0;
@@ -825,7 +843,8 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
         // a warp whose rows all end before this tile has nothing to add
         const int warp_hi = pos0 + min(rows - 1, row0 + warp * 16 + 15) / rep;
         if (tile * BN <= warp_hi && row0 + warp * 16 < rows)
-            warp_tile<BN, BM>(st, q_s, warp * 16, ring.k_stage(s), ring.v_stage(s), 0, tile * BN, pos_r, first_r, scale2, kept_r, 0, capl);
+            warp_tile<BN, BM>(st, q_s, warp * 16, ring.k_stage(s), ring.v_stage(s), 0, tile * BN, pos_r, first_r, scale2, kept_r, 0, capl,
+                              slope_r, pos_r);
     }
     ring.drain(ok ? -1 : t);
     if (!ok) {
@@ -950,15 +969,17 @@ static int check_common(const void* q, int q_stride, const void* out, int out_st
 // `sinks` (null: none): one 32-bit number per query head, one more term e^sink of every row's softmax denominator.
 // `cap` > 0: scores become cap * tanh(score / cap); `keep` > 0 (with a window): the sequence's first keys stay visible
 // behind the window.  Either sends the launch to the kernel that walks a list of tiles (decode_kernel), at every head size.
-WLLM_API int wllm_attention_mma_decode_capped(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+// `slopes` (null: none): one 32-bit number per query head; the score of key j from position p loses slope_h * (p - j), after
+// the scale and the cap.  It sends the launch to the kernel that walks a list of tiles too.
+WLLM_API int wllm_attention_mma_decode_biased(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                                               const void* v_pages, long long pool_pages, const int* req_q_start,
                                               const int* req_q_len, const int* req_ctx_len, const int* block_table,
                                               int max_pages, int requests, int nq, int nkv, int page_size, int window,
                                               float scale, int split_keys, int max_splits, float* scratch, int* status,
-                                              const float* sinks, float cap, int keep, cudaStream_t stream) {
+                                              const float* sinks, float cap, int keep, const float* slopes, cudaStream_t stream) {
     if (requests <= 0) return WLLM_OK;
     if (cap < 0.f || keep < 0 || (keep > 0 && window <= 0)) return WLLM_BAD_SIZE;
-    const bool listed = cap > 0.f || keep > 0;
+    const bool listed = cap > 0.f || keep > 0 || slopes != nullptr;
     const int bad = check_common(q, q_stride, out, out_stride, k_pages, v_pages, nq, nkv, page_size, pool_pages);
     if (bad) return bad;
     const int tile = USE_TMA ? WS_BN : BN;      // splits are whole tiles of the kernel that runs
@@ -996,11 +1017,22 @@ WLLM_API int wllm_attention_mma_decode_capped(const void* q, int q_stride, void*
         st = wllm_launch(decode_kernel, dim3(requests, nkv, max_splits), NTHREADS, DEC_SMEM, stream,
                          (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, km, vm,
                          req_q_start, req_q_len, req_ctx_len, block_table, max_pages, nq, nkv, page_size, window,
-                         scale * LOG2E, split_keys, max_splits, part_o, part_ml, status, sinks, cap * LOG2E, keep);
+                         scale * LOG2E, split_keys, max_splits, part_o, part_ml, status, sinks, cap * LOG2E, keep, slopes);
     if (st || max_splits == 1) return st;
     return wllm_launch(merge_kernel, dim3(nq, requests), HD >= 256 ? 256 : (HD >= 128 ? 128 : 64), 0, stream,
                        (bf16*)out, out_stride, req_q_start, req_q_len, req_ctx_len, nq, split_keys, max_splits,
                        (const float*)part_o, (const float*)part_ml, sinks);
+}
+
+WLLM_API int wllm_attention_mma_decode_capped(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                              const void* v_pages, long long pool_pages, const int* req_q_start,
+                                              const int* req_q_len, const int* req_ctx_len, const int* block_table,
+                                              int max_pages, int requests, int nq, int nkv, int page_size, int window,
+                                              float scale, int split_keys, int max_splits, float* scratch, int* status,
+                                              const float* sinks, float cap, int keep, cudaStream_t stream) {
+    return wllm_attention_mma_decode_biased(q, q_stride, out, out_stride, k_pages, v_pages, pool_pages, req_q_start, req_q_len,
+                                            req_ctx_len, block_table, max_pages, requests, nq, nkv, page_size, window, scale,
+                                            split_keys, max_splits, scratch, status, sinks, cap, keep, nullptr, stream);
 }
 
 WLLM_API int wllm_attention_mma_decode_sinks(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
@@ -1033,14 +1065,16 @@ WLLM_API long long wllm_attention_mma_prefill_halves_floats(int requests, int ma
 
 // Tokens of requests with q_len > 1 (and of those with q_len == 1 too unless skip_single).
 // `cap`, `keep`: as for decode; either sends the launch to the kernel that walks a list of tiles (prefill_kernel).
-WLLM_API int wllm_attention_mma_prefill_capped(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+// `slopes`: as for decode; with them the launch runs on the mma.sync kernel (the tensor-memory kernels take no bias by distance).
+WLLM_API int wllm_attention_mma_prefill_biased(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                                                const void* v_pages, long long pool_pages, const int* req_q_start,
                                                const int* req_q_len, const int* req_ctx_len, const int* block_table,
                                                int max_pages, int requests, int max_q_len, int nq, int nkv, int page_size,
                                                int window, float scale, int skip_single, int split_above, float* halves,
-                                               int* status, const float* sinks, float cap, int keep, cudaStream_t stream) {
+                                               int* status, const float* sinks, float cap, int keep, const float* slopes,
+                                               cudaStream_t stream) {
     if (cap < 0.f || keep < 0 || (keep > 0 && window <= 0)) return WLLM_BAD_SIZE;
-    const bool listed = cap > 0.f || keep > 0;
+    const bool listed = cap > 0.f || keep > 0 || slopes != nullptr;
     // split_above > 0 (tensor-memory kernel only): a tile of 128 rows that walks more than split_above tiles of
     // 64 keys is shared by two CTAs; `halves` then holds wllm_attention_mma_prefill_halves_floats(...) floats.
     if (requests <= 0 || max_q_len <= 0) return WLLM_OK;
@@ -1082,7 +1116,7 @@ WLLM_API int wllm_attention_mma_prefill_capped(const void* q, int q_stride, void
 #if (HEAD_DIM % 128 == 0)
     // more than one tile of 128 rows in the longest request: pairs of CTAs on 256-row tiles
     // (the tensor-memory kernels walk a list of key tiles too and take the cap; a launch with kept keys shares no tile)
-    if (use_tc && use_pair && max_q_len * (nq / nkv) > TC_BM && (out_stride % 8 == 0) && (((uintptr_t)out & 15) == 0)) {
+    if (slopes == nullptr && use_tc && use_pair && max_q_len * (nq / nkv) > TC_BM && (out_stride % 8 == 0) && (((uintptr_t)out & 15) == 0)) {
         const int pair_tiles = (max_q_len * (nq / nkv) + 2 * TC_BM - 1) / (2 * TC_BM);
         return wllm_launch(prefill_pair_kernel, dim3(2 * nkv, requests, pair_tiles), TC_THREADS, PR_SMEM, stream,
                            (const bf16*)q, q_stride, (bf16*)out, out_stride, km, vm, req_q_start, req_q_len, req_ctx_len,
@@ -1090,7 +1124,7 @@ WLLM_API int wllm_attention_mma_prefill_capped(const void* q, int q_stride, void
                            cap * LOG2E, keep);
     }
 #endif
-    if (use_tc && (out_stride % 8 == 0) && (((uintptr_t)out & 15) == 0)) {
+    if (slopes == nullptr && use_tc && (out_stride % 8 == 0) && (((uintptr_t)out & 15) == 0)) {
         int* arrivals = nullptr;
         if (listed) split_above = 0;
         if (split_above > 0) {
@@ -1107,7 +1141,18 @@ WLLM_API int wllm_attention_mma_prefill_capped(const void* q, int q_stride, void
     return wllm_launch(prefill_kernel, dim3(nkv, requests, tiles), PRE_THREADS, PRE_SMEM, stream,
                        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, km, vm,
                        req_q_start, req_q_len, req_ctx_len, block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E,
-                       skip_single, status, sinks, cap * LOG2E, keep);
+                       skip_single, status, sinks, cap * LOG2E, keep, slopes);
+}
+
+WLLM_API int wllm_attention_mma_prefill_capped(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                               const void* v_pages, long long pool_pages, const int* req_q_start,
+                                               const int* req_q_len, const int* req_ctx_len, const int* block_table,
+                                               int max_pages, int requests, int max_q_len, int nq, int nkv, int page_size,
+                                               int window, float scale, int skip_single, int split_above, float* halves,
+                                               int* status, const float* sinks, float cap, int keep, cudaStream_t stream) {
+    return wllm_attention_mma_prefill_biased(q, q_stride, out, out_stride, k_pages, v_pages, pool_pages, req_q_start, req_q_len,
+                                             req_ctx_len, block_table, max_pages, requests, max_q_len, nq, nkv, page_size, window,
+                                             scale, skip_single, split_above, halves, status, sinks, cap, keep, nullptr, stream);
 }
 
 WLLM_API int wllm_attention_mma_prefill_sinks(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,

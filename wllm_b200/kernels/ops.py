@@ -563,24 +563,27 @@ def decode_split_plan(heads: int, max_ctx: int, tile: int) -> tuple:
 
 def attention_mma_decode(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table, nq: int, nkv: int,
                          hd: int, page_size: int, window: int, scale: float, split_keys: int, max_splits: int,
-                         scratch: torch.Tensor, sinks: torch.Tensor | None = None, cap: float = 0.0, keep: int = 0) -> None:
+                         scratch: torch.Tensor, sinks: torch.Tensor | None = None, cap: float = 0.0, keep: int = 0,
+                         slopes: torch.Tensor | None = None) -> None:
     """bfloat16 attention of the requests that bring one token (csrc/attention_mma.cu, decode).
     `sinks`: float32 [nq], one more term e^sink of every row's softmax denominator.  `cap` > 0: scores become
-    cap * tanh(score / cap); `keep` > 0 (with a window): the sequence's first `keep` keys stay visible behind the window."""
-    _need_cuda(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table, scratch, sinks)
+    cap * tanh(score / cap); `keep` > 0 (with a window): the sequence's first `keep` keys stay visible behind the window.
+    `slopes`: float32 [nq]; the score of key j from position p loses slopes[head] * (p - j), after the scale and the cap."""
+    _need_cuda(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table, scratch, sinks, slopes)
+    assert slopes is None or (slopes.dtype == torch.float32 and slopes.shape == (nq,) and slopes.is_contiguous())
     assert sinks is None or (sinks.dtype == torch.float32 and sinks.shape == (nq,) and sinks.is_contiguous())
     assert q.dtype == torch.bfloat16 == out.dtype == k_pages.dtype and q.stride(1) == 1 and out.stride(1) == 1
     assert k_pages.is_contiguous() and v_pages.is_contiguous() and scratch.dtype == torch.float32
     R = req_q_len.shape[0]
     assert scratch.numel() >= attention_mma_scratch_floats(R, nq, hd, max_splits)
     lib = load_family("attention_mma", {"HEAD_DIM": hd})
-    _check(lib.wllm_attention_mma_decode_capped(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages),
+    _check(lib.wllm_attention_mma_decode_biased(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages),
                                                ctypes.c_longlong(k_pages.shape[0]),
                                                _ptr(_int32(req_q_start, "req_q_start")), _ptr(_int32(req_q_len, "req_q_len")),
                                                _ptr(_int32(req_ctx_len, "req_ctx_len")),
                                                _ptr(_int32(block_table, "block_table")), block_table.shape[1], R, nq, nkv,
                                                page_size, window, c_float(scale), split_keys, max_splits, _ptr(scratch),
-                                               _ptr(_status_word(q.device)), _ptr(sinks), c_float(cap), keep, _stream()),
+                                               _ptr(_status_word(q.device)), _ptr(sinks), c_float(cap), keep, _ptr(slopes), _stream()),
            f"attention_mma_decode(head_dim={hd}, heads={nq}/{nkv})")
     global launches
     launches += 1 if max_splits > 1 else 0    # the merge kernel
@@ -619,12 +622,14 @@ def prefill_share_plan(q_lens, ctx_lens, nq: int, nkv: int, hd: int, skip_single
 def attention_mma_prefill(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table, max_q_len: int,
                           nq: int, nkv: int, hd: int, page_size: int, window: int, scale: float,
                           skip_single: bool, split_above: int = 0, halves: torch.Tensor | None = None,
-                          sinks: torch.Tensor | None = None, cap: float = 0.0, keep: int = 0) -> None:
+                          sinks: torch.Tensor | None = None, cap: float = 0.0, keep: int = 0,
+                          slopes: torch.Tensor | None = None) -> None:
     """bfloat16 attention of the requests that bring several tokens (csrc/attention_mma.cu, prefill).
     split_above > 0 (head sizes in steps of 64): a tile of 128 rows that walks more than that many tiles of 64
     keys is computed by two CTAs, half of the keys each; `halves` (float32) holds their partial results.
-    `cap`, `keep`: as for attention_mma_decode; with either the mma.sync kernel that walks a list of key tiles runs."""
-    _need_cuda(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table, halves, sinks)
+    `cap`, `keep`, `slopes`: as for attention_mma_decode; with any of them the mma.sync kernel that walks a list of key tiles runs."""
+    _need_cuda(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table, halves, sinks, slopes)
+    assert slopes is None or (slopes.dtype == torch.float32 and slopes.shape == (nq,) and slopes.is_contiguous())
     assert sinks is None or (sinks.dtype == torch.float32 and sinks.shape == (nq,) and sinks.is_contiguous())
     if split_above > 0:
         assert hd % 64 == 0 and halves is not None and halves.dtype == torch.float32 and halves.is_contiguous()
@@ -632,14 +637,14 @@ def attention_mma_prefill(q, out, k_pages, v_pages, req_q_start, req_q_len, req_
     assert q.dtype == torch.bfloat16 == out.dtype == k_pages.dtype and q.stride(1) == 1 and out.stride(1) == 1
     assert k_pages.is_contiguous() and v_pages.is_contiguous()
     lib = load_family("attention_mma", {"HEAD_DIM": hd})
-    _check(lib.wllm_attention_mma_prefill_capped(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages),
+    _check(lib.wllm_attention_mma_prefill_biased(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages),
                                                 ctypes.c_longlong(k_pages.shape[0]),
                                                 _ptr(_int32(req_q_start, "req_q_start")), _ptr(_int32(req_q_len, "req_q_len")),
                                                 _ptr(_int32(req_ctx_len, "req_ctx_len")),
                                                 _ptr(_int32(block_table, "block_table")), block_table.shape[1],
                                                 req_q_len.shape[0], max_q_len, nq, nkv, page_size, window, c_float(scale),
                                                 1 if skip_single else 0, split_above, _ptr(halves) if split_above > 0 else None,
-                                                _ptr(_status_word(q.device)), _ptr(sinks), c_float(cap), keep, _stream()),
+                                                _ptr(_status_word(q.device)), _ptr(sinks), c_float(cap), keep, _ptr(slopes), _stream()),
            f"attention_mma_prefill(head_dim={hd}, heads={nq}/{nkv})")
 
 

@@ -98,8 +98,8 @@ class PagedAttention:
             raise ValueError(f"head size {self.hd_file}: heads that are divided by their root mean square come in steps of 8 elements")
         self.sink_name = spec.options.get("sink")
         self.unit_norm_eps = spec.options.get("qk_unit_norm_eps")
-        # the tensor-core kernels take keys and values of one size and no bias by distance; other cases run on the general kernels
-        self.general = self.vd != self.hd or self.slope_values is not None
+        # the tensor-core kernels take keys and values of one size; other cases run on the general kernels
+        self.general = self.vd != self.hd
         # columns of the fused q|k|v row (q alone in a mixer that reads another's keys and values), the gate's behind them
         self.qkv_width = self.nq * self.hd if self.borrows else (self.nq + self.nkv) * self.hd + self.nkv * self.vd
         self.width = self.qkv_width + (self.nq * self.vd if self.gate_name is not None else 0)
@@ -239,9 +239,10 @@ class PagedAttention:
             return
         decode = ctx.num_single > 0 and nq // nkv <= 16
         extra = {"sinks": self.sinks} if self.sinks is not None else {}
-        listed = self.softcap > 0 or self.keep_first > 0       # the kernels that walk a list of key tiles (mma.sync)
+        # the kernels that walk a list of key tiles (mma.sync) take a cap, kept first keys and a bias by distance
+        listed = self.softcap > 0 or self.keep_first > 0 or self.slopes is not None
         if listed:
-            extra.update(cap=self.softcap, keep=self.keep_first)
+            extra.update(cap=self.softcap, keep=self.keep_first, slopes=self.slopes)
         if decode:
             R = ctx.n_requests
             # one CTA fits on an SM: every (request, kv head) is cut into parts so that the CTAs finish together
