@@ -24,6 +24,10 @@ is another workload (the default one and its line are unchanged): Pesanex models
 shapes (L2 flushed before each timed launch), each with the bytes it must move over the measured copy bandwidth,
 beside the like kernel of the Gemma layer.  One JSON line.
 
+    python bench.py --design gudarax [--steps K] [--warmup W] [--batch 8] [--context 2048] [--sizes 2k,4k]
+
+Gudarax beside a Zafilix of equal layer sizes (the closest of the other designs), and its kernels one by one beside their like kernels.
+
     python bench.py --design taritar [--steps K] [--warmup W] [--batch 8] [--context 2048] [--sizes 2k,4k]
 
 the same for Taritar (several residual streams, attention with a score cap behind a window that keeps first keys, layers
@@ -942,6 +946,268 @@ def zafilix_bench(args) -> int:
     return 0
 
 
+GUDARAX_SIZES = {
+    # width, dense feed-forward, attention (heads, kv heads, head size) in a window, latent attention (heads, head size, value size, latent
+    # row, the queries' latent row), delta (value heads, query/key heads, key size, value size, taps), experts (number, chosen, width)
+    "2k": dict(width=2048, ff=8192, attn=(16, 4, 128), window=1024, latent=(16, 128, 128, 512, 768), delta=(16, 4, 128, 128, 4),
+               experts=(16, 2, 2048), side=256, vocab=32000),
+    "4k": dict(width=4096, ff=14336, attn=(32, 8, 128), window=1024, latent=(32, 128, 128, 512, 1536), delta=(32, 8, 128, 128, 4),
+               experts=(16, 2, 4096), side=256, vocab=32000),
+}
+
+
+def gudarax_config(size: dict) -> dict:
+    """Four layers: attention in a window (the first of the two that blend values), latent attention, the delta rule, attention again;
+    dense feed-forwards behind the first two, routed experts behind the others; a token input in every layer."""
+    nq, nkv, hd = size["attn"]
+    H, dim, vd, rank, q_rank = size["latent"]
+    dh, dg, dd, dv, taps = size["delta"]
+    E, top, eff = size["experts"]
+    dense = {"kind": "dense", "ff": size["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": E, "top": top}}
+    att = {"type": "attention", "mixer": {"heads": nq, "kv_heads": nkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5,
+                                          "mask": {"size": size["window"]}, "v_mix": True}}
+    lat = {"type": "latent_attention", "mixer": {"heads": H, "dim": dim, "vdim": vd, "kv_rank": rank, "q_rank": q_rank, "scale": dim ** -0.5}}
+    dlt = {"type": "delta", "mixer": {"heads": dh, "kv_heads": dg, "dim": dd, "vdim": dv, "conv": taps}}
+    return {"architecture": "Gudarax", "vocab": size["vocab"], "width": size["width"], "max_positions": 16384, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-6}, "token_side": {"dim": size["side"]},
+            "layers": [dict(att, mlp=dense), dict(lat, mlp=dense), dict(dlt, mlp=moe), dict(att, mlp=moe)]}
+
+
+def gudarax_kernel_table(size: dict, pk: dict, T: int, batch: int, context: int) -> dict:
+    """Gudarax's kernels alone at one size's shapes beside their like kernels of the framework's other designs: microseconds, the
+    time the bytes each must move (or its arithmetic) take at the measured peaks (`floor_us`), and how many times that it takes."""
+    import torch
+    from wllm_b200.kernels import ops
+    dev, bf, f32, i32 = "cuda:0", torch.bfloat16, torch.float32, torch.int32
+    flush = torch.zeros(160 << 20, dtype=f32, device=dev)
+    W = size["width"]
+    nq, nkv, hd = size["attn"]
+    H, dim, vd, rank, q_rank = size["latent"]
+    dh, dg, dd, dv, taps = size["delta"]
+    E, top, eff = size["experts"]
+    window, side = size["window"], size["side"]
+    ps = 64
+    out = {}
+
+    def row(name, fn, bytes_moved, flops=0.0):
+        us = timed_us(fn, flush)
+        floor = max(bytes_moved / (pk["hbm_gbs"] * 1e3), flops / (pk["bf16_tflops"] * 1e6))
+        out[name] = {"us": round(us, 1), "floor_us": round(floor, 2), "x_floor": round(us / max(floor, 1e-9), 1)}
+    g = torch.Generator(device=dev).manual_seed(1)
+
+    def rnd(*shape, dtype=f32, scale=1.0):
+        return (torch.randn(*shape, generator=g, device=dev, dtype=f32) * scale).to(dtype)
+    one = torch.ones(1, dtype=i32, device=dev)
+    starts, lens = torch.arange(batch, dtype=i32, device=dev), torch.ones(batch, dtype=i32, device=dev)
+    # ---- q | k | v into the pages: rows normed as wholes (Zafilix's), and with biases and blended values in front (this design's)
+    pages = batch * (-(-(context + 1) // ps)) + -(-T // ps) + 1
+    kp, vp = rnd(pages, nkv, ps, hd, dtype=bf), rnd(pages, nkv, ps, hd, dtype=bf)
+    none = torch.empty(0, dtype=f32, device=dev)
+    q_gain, k_gain = rnd(nq * hd, dtype=bf), rnd(nkv * hd, dtype=bf)
+    bias, blend = rnd((nq + 2 * nkv) * hd), torch.full((1,), 0.4, device=dev)
+    for n, tag in ((T, "prefill"), (batch, "decode")):
+        qkv = rnd(n, (nq + 2 * nkv) * hd, dtype=bf)
+        qo = torch.empty(n, nq * hd, dtype=bf, device=dev)
+        first = torch.empty(n, nkv * hd, device=dev)
+        pos = torch.arange(n, dtype=i32, device=dev)
+        moved = n * (nq + 2 * nkv) * hd * 2 * 2
+        row(f"{tag}/row norms+cache write (no turn)",
+            lambda: ops.rope_row_norm_kv_write(qkv, qo, pos, pos, none, kp, vp, nq, nkv, hd, 0, ps, q_gain, k_gain, 1e-6, nq * hd, nkv * hd), moved)
+        row(f"{tag}/biases+row norms+cache write, values left for later layers",
+            lambda: ops.rope_row_norm_kv_write(qkv, qo, pos, pos, none, kp, vp, nq, nkv, hd, 0, ps, q_gain, k_gain, 1e-6, nq * hd, nkv * hd,
+                                               bias=bias, v_first=first, mix="first"), moved + n * nkv * hd * 4)
+        row(f"{tag}/biases+row norms+cache write, values blended",
+            lambda: ops.rope_row_norm_kv_write(qkv, qo, pos, pos, none, kp, vp, nq, nkv, hd, 0, ps, q_gain, k_gain, 1e-6, nq * hd, nkv * hd,
+                                               bias=bias, v_first=first, blend=blend, mix="later"), moved + n * nkv * hd * 4)
+    # ---- attention in a window over a prompt of T tokens and for one decoded token: plain, and with the bias by distance
+    slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / nq) for h in range(nq)], dtype=f32, device=dev)
+    table = torch.arange(-(-T // ps), dtype=i32, device=dev).view(1, -1)
+    q, ao = rnd(T, nq * hd, dtype=bf), torch.empty(T, nq * hd, dtype=bf, device=dev)
+    in_window = sum(min(p + 1, window) for p in range(T))
+    for what, extra in (("attention in a window", {}), ("attention in a window with a bias by distance", {"slopes": slopes})):
+        row(f"prefill/{what}", lambda: ops.attention_mma_prefill(q, ao, kp, vp, one * 0, one * T, one * T, table, T, nq, nkv, hd, ps, window,
+                                                                 hd ** -0.5, skip_single=False, **extra), T * nq * hd * 4, 4.0 * nq * hd * in_window)
+    per = -(-(context + 1) // ps)
+    dtable = torch.arange(batch * per, dtype=i32, device=dev).view(batch, per)
+    qd, od = rnd(batch, nq * hd, dtype=bf), torch.empty(batch, nq * hd, dtype=bf, device=dev)
+    ctxs = lens * context
+    split_keys, max_splits = ops.decode_split_plan(batch * nkv, -(-context // 512) * 512, 32 if hd % 64 == 0 else 64)
+    scratch = torch.empty(ops.attention_mma_scratch_floats(batch, nq, hd, max_splits), device=dev)
+    read_w = min(context, window)
+    for what, extra in (("attention in a window", {}), ("attention in a window with a bias by distance", {"slopes": slopes})):
+        row(f"decode/{what}", lambda: ops.attention_mma_decode(qd, od, kp, vp, starts, lens, ctxs, dtable, nq, nkv, hd, ps, window, hd ** -0.5,
+                                                               split_keys, max_splits, scratch, **extra), batch * read_w * nkv * hd * 2 * 2)
+    # ---- latent attention: the cache row and the queries' latent row; the queries' products; attention over every earlier row
+    lp = rnd(pages, 1, ps, rank, dtype=bf)
+    l_gain, cq_gain = rnd(rank, dtype=bf), rnd(q_rank, dtype=bf)
+    w_uq = rnd(H * dim, q_rank, dtype=bf, scale=0.03)
+    w_uk, w_uv = rnd(H, rank, dim, dtype=bf, scale=0.05), rnd(H, vd, rank, dtype=bf, scale=0.05)
+    for n, tag in ((T, "prefill"), (batch, "decode")):
+        pos = torch.arange(n, dtype=i32, device=dev)
+        plain = rnd(n, H * dim + rank, dtype=bf)
+        q_plain, q_mapped = torch.empty(n, H * dim, dtype=bf, device=dev), torch.empty(n, H * rank, dtype=bf, device=dev)
+        row(f"{tag}/latent row (norm, cache write), queries projected directly (Zafilix's form without a turn)",
+            lambda: ops.latent_prepare(plain, 0, pos, pos, none, l_gain, 1e-6, lp, ps, None if tag == "prefill" else q_plain, q_mapped, H, dim, 0, 0,
+                                       rank, rank), n * (H * dim + rank) * 2 * 2)
+        fused = rnd(n, q_rank + rank + H * vd, dtype=bf)
+        cq = torch.empty(n, q_rank, dtype=bf, device=dev)
+        row(f"{tag}/latent row and the queries' latent row (two norms, cache write)",
+            lambda: ops.latent_prepare(fused, 0, pos, pos, none, l_gain, 1e-6, lp, ps, None, q_mapped, H, dim, 0, 0, rank, rank, q_rank=q_rank,
+                                       q_gain=cq_gain, cq_out=cq), n * (q_rank + rank) * 2 * 2)
+        qu = torch.empty(n, H * dim, dtype=bf, device=dev)
+        row(f"{tag}/latent: queries from their latent row", lambda: ops.linear(cq, w_uq, qu), H * dim * q_rank * 2 + n * (q_rank + H * dim) * 2,
+            2.0 * n * H * dim * q_rank)
+        row(f"{tag}/latent: the keys' map on the queries", lambda: ops.head_linear(qu.view(n, H, dim), w_uk, q_mapped.view(n, H, rank)),
+            H * rank * dim * 2 + n * H * (dim + rank) * 2, 2.0 * n * H * dim * rank)
+        heads_out = rnd(n, H * vd, dtype=bf)
+        row(f"{tag}/sigmoid gate on the heads' outputs", lambda: ops.sigmoid_gate(heads_out, fused, 0, q_rank + rank), n * H * vd * 2 * 3)
+    ql, mixed_l = rnd(T, H * rank, dtype=bf, scale=0.2), torch.empty(T, H * rank, dtype=bf, device=dev)
+    seen = T * (T + 1) // 2
+    if ops.latent_mma_ok(H, rank, rank, ps):
+        row("prefill/attention over latent rows (every earlier row, tensor cores)",
+            lambda: ops.latent_attention_mma(ql, mixed_l, lp, one * 0, one * T, one * T, table, T, H, rank, rank, ps, 0, dim ** -0.5),
+            T * H * 2 * rank * 2, 4.0 * H * rank * seen)
+        qdl, odl = rnd(batch, H * rank, dtype=bf, scale=0.2), torch.empty(batch, H * rank, dtype=bf, device=dev)
+        split_tiles, lat_splits = ops.latent_split_plan(batch, H, -(-context // ps) * ps, 0)
+        mscratch = torch.empty(ops.latent_mma_scratch_floats(batch, H, rank, lat_splits), device=dev)
+        row("decode/attention over latent rows (every earlier row, tensor cores, keys in splits)",
+            lambda: ops.latent_attention_mma(qdl, odl, lp, starts, lens, ctxs, dtable, 1, H, rank, rank, ps, 0, dim ** -0.5, split_tiles=split_tiles,
+                                             max_splits=lat_splits, scratch=mscratch),
+            batch * context * rank * 2 + batch * H * 2 * rank * 2, 4.0 * batch * H * rank * context)
+    # ---- recurrences: Pesanex's decayed state with a fixed decay per head, and the gated delta rule, at the same head sizes
+    GD, HV = dg * dd, dh * dv
+    Wd = 2 * GD + 2 * HV + 2 * dh
+    off = {"q": 0, "k": GD, "v": 2 * GD, "g": 2 * GD + HV, "b": 2 * GD + 2 * HV, "a": 2 * GD + 2 * HV + dh}
+    conv = [rnd(c, taps, dtype=bf) for c in (GD, GD, HV)]
+    a_log, dt_bias, nw = rnd(dh, dtype=bf), rnd(dh, dtype=bf), rnd(dv, dtype=bf)
+    head_decay = torch.full((dh,), 0.97, device=dev)
+    for n, tag, R in ((T, "prefill", 1), (batch, "decode", batch)):
+        rs, rl, rslot = (one * 0, one * n, one * 0) if R == 1 else (starts, lens, starts)
+        token_req = torch.zeros(n, dtype=i32, device=dev) if R == 1 else starts
+        pos = torch.arange(n, dtype=i32, device=dev)
+        # Pesanex's recurrence with as many query/key heads as value heads (it has no grouped form)
+        wide = rnd(n, 2 * dh * dd + 2 * HV, dtype=bf)
+        bufs = [torch.empty(n, dh * dd, device=dev), torch.empty(n, dh * dd, device=dev), torch.empty(n, HV, device=dev)]
+        row(f"{tag}/decayed state: inputs (scales, no turn)",
+            lambda: ops.linattn_prepare(wide, 0, 0, dh * dd, 2 * dh * dd, dh, dd, dv, pos, *bufs, q_scale=dd ** -0.5),
+            n * ((2 * dh * dd + HV) * 2 + (2 * dh * dd + HV) * 4))
+        state = torch.zeros(batch + 1, dh, dd, dv, device=dev)
+        o = torch.empty(n, HV, device=dev)
+        seg_len, max_seg = ops.linattn_segment_plan(n, 1, dh, dv) if R == 1 else (0, 1)
+        seg_state, seg_decay = torch.empty(R * max_seg * dh * dd * dv, device=dev), torch.empty(R * max_seg * dh * dd, device=dev)
+        row(f"{tag}/decayed state: recurrence" + (f" ({max_seg} segments of {seg_len})" if max_seg > 1 else ""),
+            lambda: ops.linattn_scan(bufs[0], bufs[1], bufs[2], None, head_decay, state, o, rs, rl, rslot, dh, dd, dv, seg_len, max_seg, seg_state,
+                                     seg_decay), n * (2 * dh * dd + 2 * HV) * 4 + R * 2 * dh * dd * dv * 4, 4.0 * n * dh * dd * dv)
+        fused = rnd(n, Wd, dtype=bf)
+        dq, dk, dvv = torch.empty(n, GD, device=dev), torch.empty(n, GD, device=dev), torch.empty(n, HV, device=dev)
+        beta, decay = torch.empty(n, dh, device=dev), torch.empty(n, dh, device=dev)
+        conv_state = torch.zeros(batch + 1, taps - 1, 2 * GD + HV, device=dev)
+        row(f"{tag}/delta rule: inputs (convolutions, SiLU, unit norms, step sizes, decays)",
+            lambda: ops.delta_prepare(fused, 0, off, dh, dg, dd, dv, taps, *conv, a_log, dt_bias, token_req, rs, rslot, conv_state, 1e-6, dd ** -0.5,
+                                      dq, dk, dvv, beta, decay), n * ((2 * GD + HV + 2 * dh) * 2 * min(taps, 2) + (2 * GD + HV + 2 * dh) * 4))
+        row(f"{tag}/delta rule: the convolutions' kept inputs",
+            lambda: ops.delta_conv_update(fused, 0, off, dh, dg, dd, dv, taps, rs, rl, rslot, conv_state), R * (taps - 1) * (2 * GD + HV) * (2 + 4))
+        dstate = torch.zeros(batch + 1, dh, dd, dv, device=dev)
+        do = torch.empty(n, HV, device=dev)
+        row(f"{tag}/delta rule: recurrence", lambda: ops.delta_scan(dq, dk, dvv, beta, decay, dstate, do, rs, rl, rslot, dh, dg, dd, dv),
+            n * (2 * GD + 2 * HV + 2 * dh) * 4 + R * 2 * dh * dd * dv * 4, 6.0 * n * dh * dd * dv)
+        gated = torch.empty(n, HV, dtype=bf, device=dev)
+        row(f"{tag}/head norm and gate", lambda: ops.head_gate_norm(do, fused, 0, off["g"], nw, 1e-6, gated, dh, dv), n * HV * (4 + 2 + 2))
+    # ---- experts: Taritar's gated clamped unit with softmax scores, and this design's (sigmoid scores on the inputs, no gate, squared ReLU)
+    for n, tag in ((T, "prefill"), (batch, "decode")):
+        x = rnd(n, W, dtype=bf)
+        wr = rnd(E, W, scale=0.05)
+        chosen, weights = torch.empty(n, top, dtype=i32, device=dev), torch.empty(n, top, device=dev)
+        for scores in ("softmax", "sigmoid"):
+            row(f"{tag}/router ({scores} scores, choice)", lambda: ops.moe_route(x, wr, None, chosen, weights, None, 1, 1, scores=scores),
+                n * W * 2 + E * W * 4)
+        pairs = n * top
+        count, offset = torch.empty(E, dtype=i32, device=dev), torch.empty(E + 1, dtype=i32, device=dev)
+        order, place = torch.empty(pairs, dtype=i32, device=dev), torch.empty(pairs, dtype=i32, device=dev)
+        tiles = torch.empty(1 + 3 * ops.moe_row_tiles(pairs, E), dtype=i32, device=dev)
+        plan_scratch = torch.empty(ops.MOE_PLAN_SEGMENTS * E, dtype=i32, device=dev)
+        ops.moe_plan(chosen, count, offset, order, place, tiles, plan_scratch)
+        w_gu, w_u, w_d = rnd(E, 2 * eff, W, dtype=bf, scale=0.02), rnd(E, eff, W, dtype=bf, scale=0.02), rnd(E, W, eff, dtype=bf, scale=0.02)
+        act, y = torch.empty(pairs, eff, dtype=bf, device=dev), torch.empty(pairs, W, device=dev)
+        used = min(E, pairs)
+        flat = weights.view(-1)
+        if pairs >= 1024:
+            xs = torch.empty(pairs, W, dtype=bf, device=dev)
+            row(f"{tag}/experts: the tokens' rows into sorted order", lambda: ops.moe_gather(x, order, top, xs), pairs * W * 4)
+            row(f"{tag}/experts: the tokens' rows into sorted order, times their scores", lambda: ops.moe_gather(x, order, top, xs, row_weights=flat),
+                pairs * W * 4)
+            row(f"{tag}/experts: gate|up with the clamped unit (grouped, tensor memory)",
+                lambda: ops.gemm_bf16_tc_grouped(xs, w_gu, act, tiles, True, 7.0, 1.702), used * 2 * eff * W * 2 + pairs * (W + eff) * 2, 4.0 * pairs * eff * W)
+            row(f"{tag}/experts: up with the squared ReLU (grouped, tensor memory)",
+                lambda: ops.gemm_bf16_tc_grouped(xs, w_u, act, tiles, False, unit="relu_squared"), used * eff * W * 2 + pairs * (W + eff) * 2,
+                2.0 * pairs * eff * W)
+            row(f"{tag}/experts: down (grouped, tensor memory)", lambda: ops.gemm_bf16_tc_grouped(act, w_d, y, tiles, False),
+                used * eff * W * 2 + pairs * (eff * 2 + W * 4), 2.0 * pairs * eff * W)
+        else:
+            row(f"{tag}/experts: gate|up with the clamped unit (grouped, mma.sync)", lambda: ops.moe_grouped(x, w_gu, act, offset, order, top, True, 7.0, 1.702),
+                used * 2 * eff * W * 2 + pairs * (W + eff) * 2, 4.0 * pairs * eff * W)
+            row(f"{tag}/experts: up with the squared ReLU on scored inputs (grouped, mma.sync)",
+                lambda: ops.moe_grouped(x, w_u, act, offset, order, top, False, unit="relu_squared", row_weights=flat),
+                used * eff * W * 2 + pairs * (W + eff) * 2, 2.0 * pairs * eff * W)
+            row(f"{tag}/experts: down (grouped, mma.sync)", lambda: ops.moe_grouped(act, w_d, y, offset, order, top, False),
+                used * eff * W * 2 + pairs * (eff * 2 + W * 4), 2.0 * pairs * eff * W)
+        o32 = torch.empty(n, W, device=dev)
+        row(f"{tag}/experts' outputs weighted and summed", lambda: ops.moe_combine(y, place, weights, None, None, o32), pairs * W * 4 + n * W * 4)
+        row(f"{tag}/experts' outputs summed as they are", lambda: ops.moe_combine(y, place, None, None, None, o32), pairs * W * 4 + n * W * 4)
+    # ---- the token's own input: the gate on the table row (beside the gated activation of a feed-forward of that width)
+    tbl = rnd(size["vocab"], side, dtype=bf)
+    for n, tag in ((T, "prefill"), (batch, "decode")):
+        ids = torch.randint(0, size["vocab"], (n,), generator=g, device=dev, dtype=i32)
+        z, gu = rnd(n, side, dtype=bf), rnd(n, 2 * side, dtype=bf)
+        tg = torch.empty(n, side, dtype=bf, device=dev)
+        row(f"{tag}/gated activation of a feed-forward of the token input's width", lambda: ops.gated_act(gu, tg, "gelu_tanh"), n * side * 2 * 3)
+        row(f"{tag}/token input: gelu_tanh of the projection times the table row", lambda: ops.token_gate(z, 0, ids, tbl, "gelu_tanh", tg), n * side * 2 * 3)
+    return out
+
+
+def gudarax_bench(args) -> int:
+    import torch
+    from wllm_b200.config import EngineConfig, GudaraxConfig, ZafilixConfig
+    from wllm_b200.engine import build_model
+    pk = peaks()
+    ps, T = args.page_size, 2048
+    context = args.context or 2048
+    engine_cfg = EngineConfig(dtype="bfloat16", block_size=ps, max_num_seqs=max(64, args.batch), cuda_graphs=not args.no_graphs)
+    sizes = {}
+    for name in (args.sizes if args.sizes != "2b,7b" else "2k,4k").split(","):
+        size = GUDARAX_SIZES[name]
+        nq, nkv, hd = size["attn"]
+        H, dim, vd, rank, _ = size["latent"]
+        # the closest existing design at equal sizes: Zafilix (attention with whole-row norms, in blocks of the window's size; latent
+        # attention in a window of that size with a turning part of 64), dense feed-forwards of the dense width
+        zaf = dict(ZAFILIX_SIZES[name], width=size["width"], ff=size["ff"], attn=(nq, nkv, hd), block=size["window"],
+                   latent=(H, dim, 64, vd, rank), window=size["window"], vocab=size["vocab"])
+        models = {"zafilix": ZafilixConfig.from_dict(zafilix_config(zaf)), "gudarax": GudaraxConfig.from_dict(gudarax_config(size))}
+        res = {}
+        for label, cfg in models.items():
+            model = build_model(None, engine_cfg.dtype, engine_cfg.device, config=cfg, random_seed=1)
+            pre_ms = prefill_run(model, engine_cfg, T, ps)
+            ms, launches, _, clocks, _ = decode_run(model, engine_cfg, args.batch, context, min(args.steps, 32), args.warmup, ps, 3)
+            res[label] = {"weights_gb": round(model.weight_bytes() / 1e9, 3), "prefill_tok_s": round(T / (pre_ms / 1e3), 1),
+                          "prefill_ms": round(pre_ms, 3), "decode_tok_s": round(args.batch / (ms / 1e3), 1),
+                          "decode_ms_per_step": round(ms, 4), "decode_launches": launches,
+                          "decode_weights_hbm_frac": round(model.weight_bytes() / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 3), "clocks": clocks}
+            del model
+            torch.cuda.empty_cache()
+        sizes[name] = {"shape": size, "models": res}
+        if not args.no_points:
+            sizes[name]["kernels"] = gudarax_kernel_table(size, pk, T, args.batch, context)
+    print(json.dumps({"metric": "Gudarax beside Zafilix at equal layer sizes: prefill tok/s @ 2048 tokens, decode tok/s",
+                      "design": "gudarax", "unit": "tokens/s", "n_gpus": 1, "steps": min(args.steps, 32), "warmup": args.warmup,
+                      "dtype": "bf16", "data": "synthetic (random weights, random token ids, random cached keys/values)",
+                      "config": {"global_batch": args.batch, "seq_len": context, "prefill_tokens": T, "page_size": ps,
+                                 "cuda_graphs": not args.no_graphs, "peaks": pk["source"],
+                                 "l2": "kernel table: a 640 MB buffer is written before every timed launch"},
+                      "peaks": pk, "sizes": sizes}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -956,9 +1222,9 @@ def main() -> int:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--regions", type=int, default=5, help="timed regions of --steps steps each; the median is reported")
-    ap.add_argument("--design", default="gemma", choices=["gemma", "pesanex", "taritar", "zafilix"],
-                    help="gemma: the default workload; pesanex, taritar, zafilix: models of that design beside a Gemma of equal layer sizes (another line)")
-    ap.add_argument("--sizes", default="2b,7b", help="which of the layer sizes to run (--design pesanex: 2b, 7b; taritar, zafilix: 2k, 4k)")
+    ap.add_argument("--design", default="gemma", choices=["gemma", "pesanex", "taritar", "zafilix", "gudarax"],
+                    help="gemma: the default workload; pesanex, taritar, zafilix, gudarax: models of that design beside a Gemma of equal layer sizes (another line)")
+    ap.add_argument("--sizes", default="2b,7b", help="which of the layer sizes to run (--design pesanex: 2b, 7b; taritar, zafilix, gudarax: 2k, 4k)")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
@@ -972,6 +1238,8 @@ def main() -> int:
         return taritar_bench(args)
     if args.design == "zafilix":
         return zafilix_bench(args)
+    if args.design == "gudarax":
+        return gudarax_bench(args)
     import torch
     from wllm_b200.config import EngineConfig, GemmaConfig
     from wllm_b200.engine import build_model

@@ -14,10 +14,10 @@
 //                           slabs): convolution and SiLU of q, k and v, the unit norms x / sqrt(sum(x^2) + eps) (q also times
 //                           q_scale), beta = sigmoid(b), g = exp(-exp(A_log) softplus(a + dt_bias)), all 32-bit.  A warp a head.
 //   wllm_delta_conv_update  the slots' last taps - 1 inputs after this step's tokens (a thread a channel, read first, written after).
-//   wllm_delta_scan         the recurrence.  The columns of S do not meet: column j needs S[:, j] alone.  Eight lanes hold a
-//                           column (key channels lane, lane + 8, ..), a warp four columns, a CTA of eight warps 32 columns of one
-//                           (request, head); tokens arrive in tiles through shared memory and are walked in order.  With
-//                           a = S^T k and b = S^T q taken from the decayed state in one pass (two sums over eight lanes),
+//   wllm_delta_scan         the recurrence.  The columns of S do not meet: column j needs S[:, j] alone.  Eight or sixteen lanes
+//                           hold a column (runs of four key channels each), a CTA of eight warps 32 or 16 columns of one
+//                           (request, head); tokens arrive in tiles through a cp.async ring and are walked in order.  With
+//                           a = S^T k and b = S^T q taken from the decayed state in one pass (two sums over a column's lanes),
 //                           u = beta (v - g a) and o = g b + u (k . q): the read-out sees the token's own write.
 #include "common.cuh"
 
@@ -130,90 +130,170 @@ delta_conv_update_kernel(const void* __restrict__ fused, int in_dtype, int row_s
 }
 
 constexpr int DR_TT = 16;          // tokens of a tile
-constexpr int DR_COLS = 32;        // value columns of a CTA: four a warp, eight lanes a column
+constexpr int DR_THREADS = 256;    // eight warps; with LPC lanes a column a warp holds 32 / LPC columns, a CTA 256 / LPC
 
-// NE: key channels a lane holds (dim <= 8 * NE).  grid (ceil(V / 32), H, requests), 256 threads.
-template <int NE>
-__global__ void __launch_bounds__(256)
+__device__ __forceinline__ void dr_cp4(float* smem_dst, const float* src) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void dr_cp16(float* smem_dst, const float* src) {      // both 16-byte aligned
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+
+// One token of the walk for the lane's NE key channels of its column (see the kernel below).
+template <int NE, int LPC>
+__device__ __forceinline__ void delta_token(float (&S)[NE], const float* __restrict__ kr, const float* __restrict__ qr, int sub, float gt,
+                                            float bt, float vt, float kq, float& o) {
+    // the lane's channels: 4 sub + 4 LPC j + e (j < NE / 4, e < 4): a column's lanes read runs of 128 contiguous bytes a load
+    float kv[NE], a4[4] = {0.f, 0.f, 0.f, 0.f}, b4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < NE / 4; ++j) {
+        const float4 k4 = *reinterpret_cast<const float4*>(kr + 4 * sub + 4 * LPC * j);
+        const float4 q4 = *reinterpret_cast<const float4*>(qr + 4 * sub + 4 * LPC * j);
+        kv[4 * j] = k4.x; kv[4 * j + 1] = k4.y; kv[4 * j + 2] = k4.z; kv[4 * j + 3] = k4.w;
+        a4[0] = fmaf(S[4 * j], k4.x, a4[0]); a4[1] = fmaf(S[4 * j + 1], k4.y, a4[1]);
+        a4[2] = fmaf(S[4 * j + 2], k4.z, a4[2]); a4[3] = fmaf(S[4 * j + 3], k4.w, a4[3]);
+        b4[0] = fmaf(S[4 * j], q4.x, b4[0]); b4[1] = fmaf(S[4 * j + 1], q4.y, b4[1]);
+        b4[2] = fmaf(S[4 * j + 2], q4.z, b4[2]); b4[3] = fmaf(S[4 * j + 3], q4.w, b4[3]);
+    }
+    float a = (a4[0] + a4[1]) + (a4[2] + a4[3]), b = (b4[0] + b4[1]) + (b4[2] + b4[3]);
+#pragma unroll
+    for (int off = 1; off < LPC; off <<= 1) {
+        a += __shfl_xor_sync(0xffffffffu, a, off);
+        b += __shfl_xor_sync(0xffffffffu, b, off);
+    }
+    const float u = bt * (vt - gt * a);
+#pragma unroll
+    for (int i = 0; i < NE; ++i) S[i] = fmaf(kv[i], u, gt * S[i]);
+    o = fmaf(u, kq, gt * b);
+}
+
+// LPC lanes hold a column, NE key channels each (dim <= LPC * NE, in runs of four).  grid (ceil(V / (256 / LPC)), H, requests),
+// 256 threads.  The walk is one dependent chain a token (two sums over a column's lanes, the step, the update); a warp alone on
+// its scheduler waits out every link of it, so heads of 64 channels and more spread a column over sixteen lanes: half the
+// instructions a warp and token, twice the warps (one warp a scheduler issued a third of the time; profiles/delta_scan_2048.txt).
+// Tiles of DR_TT tokens come through a ring of two cp.async stages, so that the
+// next tile's rows are on their way while this one is walked; a key's and a query's rows are padded with zeros to 32 NE / 4
+// channels in shared memory, so the walk carries no guards.  k . q of a tile's tokens is worked out once a tile by the
+// warps together (it is the same for every column).
+template <int NE, int LPC>
+__global__ void __launch_bounds__(DR_THREADS)
 delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                   const float* __restrict__ beta, const float* __restrict__ decay, float* __restrict__ state,
                   float* __restrict__ out, const int* __restrict__ req_q_start, const int* __restrict__ req_q_len,
                   const int* __restrict__ req_slot, int H, int G, int D, int V) {
-    extern __shared__ float dr_smem[];         // [TT][D] q, [TT][D] k, [TT][32] v, [TT] beta, [TT] decay, [TT] k.q
+    constexpr int DP = LPC * NE;                        // channels of a row in shared memory
+    constexpr int DR_COLS = DR_THREADS / LPC;           // value columns of the CTA
+    extern __shared__ __align__(16) float dr_smem[];    // two stages of [TT][DP] q, [TT][DP] k, [TT][16] v, [TT] beta, [TT] decay; [TT] k.q
     pdl_begin();
     const int r = blockIdx.z, h = blockIdx.y;
     const int len = req_q_len[r], slot = req_slot[r];
     if (len <= 0 || slot < 0) return;                      // a request that brings no token
     const int g = h / (H / G), t0 = req_q_start[r];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, sub = lane & 7;
-    const int col = blockIdx.x * DR_COLS + warp * 4 + (lane >> 3);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, sub = lane & (LPC - 1);
+    const int col0 = blockIdx.x * DR_COLS, mine = threadIdx.x / LPC, col = col0 + mine;
     const bool live = col < V;
-    float* qs = dr_smem;
-    float* ks = qs + DR_TT * D;
-    float* vs = ks + DR_TT * D;
-    float* bs = vs + DR_TT * DR_COLS;
-    float* gs = bs + DR_TT;
-    float* kq = gs + DR_TT;
+    constexpr int per_stage = DR_TT * (2 * DP + DR_COLS + 2);
+    float* kq = dr_smem + 2 * per_stage;
+    const bool wide = (D & 3) == 0 && (V & 3) == 0 && ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15) == 0);
+    if (D < DP)          // the channels behind the head's own stay zero in both stages
+        for (int idx = threadIdx.x; idx < 2 * 2 * DR_TT * (DP - D); idx += blockDim.x) {
+            const int row = idx / (DP - D), c = D + idx % (DP - D);
+            dr_smem[(row / (2 * DR_TT)) * per_stage + (row % (2 * DR_TT)) * DP + c] = 0.f;
+        }
+    auto load_tile = [&](int tile, int stage) {
+        float* qs = dr_smem + stage * per_stage;
+        float* ks = qs + DR_TT * DP;
+        float* vs = ks + DR_TT * DP;
+        float* bs = vs + DR_TT * DR_COLS;
+        float* gs = bs + DR_TT;
+        const int first = t0 + tile * DR_TT, count = min(DR_TT, len - tile * DR_TT);
+        if (wide) {
+            const int per_row = D >> 2;
+            for (int idx = threadIdx.x; idx < count * per_row; idx += blockDim.x) {
+                const int tt = idx / per_row, c = (idx - tt * per_row) * 4;
+                const size_t at = ((size_t)(first + tt) * G + g) * D + c;
+                dr_cp16(qs + tt * DP + c, q + at);
+                dr_cp16(ks + tt * DP + c, k + at);
+            }
+            for (int idx = threadIdx.x; idx < count * (DR_COLS / 4); idx += blockDim.x) {
+                const int tt = idx / (DR_COLS / 4), cc = (idx % (DR_COLS / 4)) * 4;
+                const float* vrow = v + ((size_t)(first + tt) * H + h) * V;
+                if (col0 + cc + 3 < V) dr_cp16(vs + tt * DR_COLS + cc, vrow + col0 + cc);
+                else
+                    for (int e = 0; e < 4; ++e) dr_cp4(vs + tt * DR_COLS + cc + e, vrow + min(col0 + cc + e, V - 1));
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < count * D; idx += blockDim.x) {
+                const int tt = idx / D, c = idx - tt * D;
+                const size_t at = ((size_t)(first + tt) * G + g) * D + c;
+                dr_cp4(qs + tt * DP + c, q + at);
+                dr_cp4(ks + tt * DP + c, k + at);
+            }
+            for (int idx = threadIdx.x; idx < count * DR_COLS; idx += blockDim.x) {
+                const int tt = idx / DR_COLS, cc = idx % DR_COLS;
+                dr_cp4(vs + idx, v + ((size_t)(first + tt) * H + h) * V + min(col0 + cc, V - 1));
+            }
+        }
+        if (threadIdx.x < count) {
+            dr_cp4(bs + threadIdx.x, beta + (size_t)(first + threadIdx.x) * H + h);
+            dr_cp4(gs + threadIdx.x, decay + (size_t)(first + threadIdx.x) * H + h);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
     float S[NE];
     float* Sg = state + (((size_t)slot * H + h) * D) * V;
 #pragma unroll
     for (int i = 0; i < NE; ++i) {
-        const int c = sub + 8 * i;
+        const int c = 4 * sub + 4 * LPC * (i >> 2) + (i & 3);
         S[i] = (live && c < D) ? Sg[(size_t)c * V + col] : 0.f;
     }
-    for (int tile = 0; tile < len; tile += DR_TT) {
-        const int count = min(DR_TT, len - tile);
-        __syncthreads();                                   // the tile before is read to its end
-        for (int idx = threadIdx.x; idx < count * D; idx += blockDim.x) {
-            const int tt = idx / D, c = idx - tt * D;
-            const size_t at = ((size_t)(t0 + tile + tt) * G + g) * D + c;
-            qs[tt * D + c] = q[at];
-            ks[tt * D + c] = k[at];
+    const int tiles = (len + DR_TT - 1) / DR_TT;
+    load_tile(0, 0);
+    for (int tile = 0; tile < tiles; ++tile) {
+        const int stage = tile & 1;
+        if (tile + 1 < tiles) {
+            load_tile(tile + 1, stage ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
-        for (int idx = threadIdx.x; idx < count * DR_COLS; idx += blockDim.x) {
-            const int tt = idx / DR_COLS, cc = idx % DR_COLS, j = blockIdx.x * DR_COLS + cc;
-            vs[idx] = j < V ? v[((size_t)(t0 + tile + tt) * H + h) * V + j] : 0.f;
-        }
-        if (threadIdx.x < count) {
-            bs[threadIdx.x] = beta[(size_t)(t0 + tile + threadIdx.x) * H + h];
-            gs[threadIdx.x] = decay[(size_t)(t0 + tile + threadIdx.x) * H + h];
-        }
-        __syncthreads();
-        for (int tt = warp; tt < count; tt += 8) {         // k . q of every token of the tile: a lane's strided chain, the warp's tree
+        __syncthreads();                                   // the tile is here for everyone (and the zeros behind the heads, the first time)
+        const float* qs = dr_smem + stage * per_stage;
+        const float* ks = qs + DR_TT * DP;
+        const float* vs = ks + DR_TT * DP;
+        const float* bs = vs + DR_TT * DR_COLS;
+        const float* gs = bs + DR_TT;
+        const int count = min(DR_TT, len - tile * DR_TT);
+        for (int tt = warp; tt < count; tt += DR_THREADS / 32) {     // k . q: a lane's strided chain, the warp's tree
             float acc = 0.f;
-            for (int c = lane; c < D; c += 32) acc = fmaf(ks[tt * D + c], qs[tt * D + c], acc);
+            for (int c = lane; c < D; c += 32) acc = fmaf(ks[tt * DP + c], qs[tt * DP + c], acc);
             acc = warp_sum(acc);
             if (lane == 0) kq[tt] = acc;
         }
         __syncthreads();
-        for (int tt = 0; tt < count; ++tt) {
-            const float* kr = ks + tt * D;
-            const float* qr = qs + tt * D;
-            float a = 0.f, b = 0.f, kv[NE];
-#pragma unroll
-            for (int i = 0; i < NE; ++i) {
-                const int c = sub + 8 * i;
-                kv[i] = c < D ? kr[c] : 0.f;
-                const float qv = c < D ? qr[c] : 0.f;
-                a = fmaf(S[i], kv[i], a);
-                b = fmaf(S[i], qv, b);
+        float* orow = out + ((size_t)(t0 + tile * DR_TT) * H + h) * V + col;
+        if (count == DR_TT) {
+#pragma unroll 4
+            for (int tt = 0; tt < DR_TT; ++tt) {
+                float o;
+                delta_token<NE, LPC>(S, ks + tt * DP, qs + tt * DP, sub, gs[tt], bs[tt], vs[tt * DR_COLS + mine], kq[tt], o);
+                if (live && sub == 0) orow[(size_t)tt * H * V] = o;
             }
-#pragma unroll
-            for (int o = 1; o < 8; o <<= 1) {
-                a += __shfl_xor_sync(0xffffffffu, a, o);
-                b += __shfl_xor_sync(0xffffffffu, b, o);
+        } else {
+            for (int tt = 0; tt < count; ++tt) {
+                float o;
+                delta_token<NE, LPC>(S, ks + tt * DP, qs + tt * DP, sub, gs[tt], bs[tt], vs[tt * DR_COLS + mine], kq[tt], o);
+                if (live && sub == 0) orow[(size_t)tt * H * V] = o;
             }
-            const float gt = gs[tt];
-            const float u = bs[tt] * (vs[tt * DR_COLS + warp * 4 + (lane >> 3)] - gt * a);
-#pragma unroll
-            for (int i = 0; i < NE; ++i) S[i] = fmaf(kv[i], u, gt * S[i]);
-            if (live && sub == 0) out[((size_t)(t0 + tile + tt) * H + h) * V + col] = fmaf(u, kq[tt], gt * b);
         }
+        __syncthreads();                                   // the stage and k . q are read to their end before the next tile overwrites them
     }
     if (live) {
 #pragma unroll
         for (int i = 0; i < NE; ++i) {
-            const int c = sub + 8 * i;
+            const int c = 4 * sub + 4 * LPC * (i >> 2) + (i & 3);
             if (c < D) Sg[(size_t)c * V + col] = S[i];
         }
     }
@@ -258,13 +338,21 @@ WLLM_API int wllm_delta_scan(const float* q, const float* k, const float* v, con
                              int G, int D, int V, cudaStream_t stream) {
     if (requests <= 0) return WLLM_OK;
     if (H <= 0 || H > 65535 || G <= 0 || H % G != 0 || requests > 65535 || D <= 0 || D > 256 || V <= 0) return WLLM_BAD_SIZE;
-    const dim3 grid((V + DR_COLS - 1) / DR_COLS, H, requests);
-    const size_t smem = ((size_t)DR_TT * (2 * D + DR_COLS + 3)) * sizeof(float);
-#define SCAN(NE) wllm_launch(delta_scan_kernel<NE>, grid, 256, smem, stream, q, k, v, beta, decay, state, out, req_q_start, req_q_len, \
-                             req_slot, H, G, D, V)
-    if (D <= 32) return SCAN(4);
-    if (D <= 64) return SCAN(8);
-    if (D <= 128) return SCAN(16);
-    return SCAN(32);
+    // heads of up to 32 channels: eight lanes a column, four channels each; above: sixteen lanes, 4, 8 or 16 channels each
+    const int lpc = D <= 32 ? 8 : 16, ne = D <= 64 ? 4 : (D <= 128 ? 8 : 16), cols = DR_THREADS / lpc;
+    const dim3 grid((V + cols - 1) / cols, H, requests);
+    const size_t smem = ((size_t)2 * DR_TT * (2 * lpc * ne + cols + 2) + DR_TT) * sizeof(float);
+    static bool raised = false;
+    if (!raised && smem > 48 * 1024) {
+        const cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<16, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        if (e != cudaSuccess) return 1000 + (int)e;
+        raised = true;
+    }
+#define SCAN(NE, LPC) wllm_launch(delta_scan_kernel<NE, LPC>, grid, DR_THREADS, smem, stream, q, k, v, beta, decay, state, out, \
+                                  req_q_start, req_q_len, req_slot, H, G, D, V)
+    if (D <= 32) return SCAN(4, 8);
+    if (D <= 64) return SCAN(4, 16);
+    if (D <= 128) return SCAN(8, 16);
+    return SCAN(16, 16);
 #undef SCAN
 }
