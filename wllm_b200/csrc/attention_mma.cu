@@ -1065,7 +1065,7 @@ WLLM_API long long wllm_attention_mma_prefill_halves_floats(int requests, int ma
 
 // Tokens of requests with q_len > 1 (and of those with q_len == 1 too unless skip_single).
 // `cap`, `keep`: as for decode; either sends the launch to the kernel that walks a list of tiles (prefill_kernel).
-// `slopes`: as for decode; with them the launch runs on the mma.sync kernel (the tensor-memory kernels take no bias by distance).
+// `slopes`: as for decode; the tensor-memory kernels take them as they take the cap (no tile is shared by two CTAs then).
 WLLM_API int wllm_attention_mma_prefill_biased(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                                                const void* v_pages, long long pool_pages, const int* req_q_start,
                                                const int* req_q_len, const int* req_ctx_len, const int* block_table,
@@ -1116,15 +1116,15 @@ WLLM_API int wllm_attention_mma_prefill_biased(const void* q, int q_stride, void
 #if (HEAD_DIM % 128 == 0)
     // more than one tile of 128 rows in the longest request: pairs of CTAs on 256-row tiles
     // (the tensor-memory kernels walk a list of key tiles too and take the cap; a launch with kept keys shares no tile)
-    if (slopes == nullptr && use_tc && use_pair && max_q_len * (nq / nkv) > TC_BM && (out_stride % 8 == 0) && (((uintptr_t)out & 15) == 0)) {
+    if (use_tc && use_pair && max_q_len * (nq / nkv) > TC_BM && (out_stride % 8 == 0) && (((uintptr_t)out & 15) == 0)) {
         const int pair_tiles = (max_q_len * (nq / nkv) + 2 * TC_BM - 1) / (2 * TC_BM);
         return wllm_launch(prefill_pair_kernel, dim3(2 * nkv, requests, pair_tiles), TC_THREADS, PR_SMEM, stream,
                            (const bf16*)q, q_stride, (bf16*)out, out_stride, km, vm, req_q_start, req_q_len, req_ctx_len,
                            block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E, skip_single, status, sinks,
-                           cap * LOG2E, keep);
+                           cap * LOG2E, keep, slopes);
     }
 #endif
-    if (slopes == nullptr && use_tc && (out_stride % 8 == 0) && (((uintptr_t)out & 15) == 0)) {
+    if (use_tc && (out_stride % 8 == 0) && (((uintptr_t)out & 15) == 0)) {
         int* arrivals = nullptr;
         if (listed) split_above = 0;
         if (split_above > 0) {
@@ -1135,7 +1135,7 @@ WLLM_API int wllm_attention_mma_prefill_biased(const void* q, int q_stride, void
         return wllm_launch(prefill_tc_kernel, dim3(nkv, requests, split_above > 0 ? 2 * tiles : tiles), TC_THREADS, TC_SMEM, stream,
                            (const bf16*)q, q_stride, (bf16*)out, out_stride, km, vm, req_q_start, req_q_len, req_ctx_len,
                            block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E, skip_single, split_above, halves,
-                           arrivals, status, sinks, cap * LOG2E, keep);
+                           arrivals, status, sinks, cap * LOG2E, keep, slopes);
     }
 #endif
     return wllm_launch(prefill_kernel, dim3(nkv, requests, tiles), PRE_THREADS, PRE_SMEM, stream,

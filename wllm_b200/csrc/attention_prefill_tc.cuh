@@ -50,7 +50,8 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
                   const int* __restrict__ req_q_start, const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_len,
                   const int* __restrict__ block_table, int max_pages, int nq, int nkv, int page_size, int window, float scale2,
                   int skip_single, int split_above, float* __restrict__ halves, int* __restrict__ arrivals,
-                  int* __restrict__ status, const float* __restrict__ sinks, float capl, int keep) {
+                  int* __restrict__ status, const float* __restrict__ sinks, float capl, int keep,
+                  const float* __restrict__ slopes) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ int s_second;
     pdl_begin();
@@ -214,7 +215,11 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
         const int pos_row = m_row < rows ? pos0 + m_row / rep : -1;            // a row past the end sees no key
         int first_row = first_visible_key(pos_row, window), kept_row = 0;
         if (keep > 0) { if (first_row <= keep) first_row = 0; else kept_row = keep; }
-        const float sc = capl > 0.f ? 1.0f : scale2;          // capped scores are in log2 units already
+        // `slopes` (null: none): the score of a key loses slope_h * (p - key), after the scale and the cap; such scores are
+        // brought to log2 units where the bias is taken off, as capped scores are
+        const float slope2 = (slopes != nullptr && m_row < rows) ? slopes[g * rep + m_row % rep] * LOG2E : 0.f;
+        const float sc = (capl > 0.f || slopes != nullptr) ? 1.0f : scale2;          // capped and biased scores are in log2 units already
+        const float pre = capl > 0.f ? 1.0f : scale2;
         const float cap_in = capl > 0.f ? 2.0f * scale2 / capl : 0.f;
         float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
@@ -233,6 +238,11 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
 #pragma unroll
                 for (int c = 0; c < 64; ++c)
                     sv[c >> 5][c & 31] = __float_as_uint(capl * (1.0f - __fdividef(2.0f, 1.0f + __expf(__uint_as_float(sv[c >> 5][c & 31]) * cap_in))));
+            }
+            if (slopes != nullptr) {
+#pragma unroll
+                for (int c = 0; c < 64; ++c)
+                    sv[c >> 5][c & 31] = __float_as_uint(fmaf(-slope2, (float)(pos_row - (key0 + c)), __uint_as_float(sv[c >> 5][c & 31]) * pre));
             }
             const bool inner = __all_sync(0xffffffffu, key0 + TC_BN - 1 <= pos_row && (key0 >= first_row || key0 + TC_BN <= kept_row));
             // One warp runs alone on its scheduler, so a chain of dependent maxima or additions would cost its
@@ -434,7 +444,8 @@ prefill_pair_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
                     const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                     const int* __restrict__ req_q_start, const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_len,
                     const int* __restrict__ block_table, int max_pages, int nq, int nkv, int page_size, int window, float scale2,
-                    int skip_single, int* __restrict__ status, const float* __restrict__ sinks, float capl, int keep) {
+                    int skip_single, int* __restrict__ status, const float* __restrict__ sinks, float capl, int keep,
+                  const float* __restrict__ slopes) {
     extern __shared__ unsigned char smem_raw[];
     pdl_begin();
     // grid (2 x key/value heads, requests, tiles): the pairs start in the order x, y, z, the tiles that walk the most
@@ -600,7 +611,11 @@ prefill_pair_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
         const int pos_row = m_row < rows ? pos0 + m_row / rep : -1;            // a row past the end sees no key
         int first_row = first_visible_key(pos_row, window), kept_row = 0;
         if (keep > 0) { if (first_row <= keep) first_row = 0; else kept_row = keep; }
-        const float sc = capl > 0.f ? 1.0f : scale2;          // capped scores are in log2 units already
+        // `slopes` (null: none): the score of a key loses slope_h * (p - key), after the scale and the cap; such scores are
+        // brought to log2 units where the bias is taken off, as capped scores are
+        const float slope2 = (slopes != nullptr && m_row < rows) ? slopes[g * rep + m_row % rep] * LOG2E : 0.f;
+        const float sc = (capl > 0.f || slopes != nullptr) ? 1.0f : scale2;          // capped and biased scores are in log2 units already
+        const float pre = capl > 0.f ? 1.0f : scale2;
         const float cap_in = capl > 0.f ? 2.0f * scale2 / capl : 0.f;
         float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
@@ -616,6 +631,11 @@ prefill_pair_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
 #pragma unroll
                 for (int c = 0; c < PR_BN; ++c)
                     sv[c >> 5][c & 31] = __float_as_uint(capl * (1.0f - __fdividef(2.0f, 1.0f + __expf(__uint_as_float(sv[c >> 5][c & 31]) * cap_in))));
+            }
+            if (slopes != nullptr) {
+#pragma unroll
+                for (int c = 0; c < PR_BN; ++c)
+                    sv[c >> 5][c & 31] = __float_as_uint(fmaf(-slope2, (float)(pos_row - (key0 + c)), __uint_as_float(sv[c >> 5][c & 31]) * pre));
             }
             const bool inner = __all_sync(0xffffffffu, key0 + PR_BN - 1 <= pos_row && (key0 >= first_row || key0 + PR_BN <= kept_row));
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};

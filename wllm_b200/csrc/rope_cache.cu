@@ -436,7 +436,8 @@ rope_row_norm_vec_kernel(const bf16* __restrict__ qkv, int row_stride, bf16* __r
                          const int* __restrict__ positions, const int* __restrict__ slots, const float* __restrict__ inv_freq,
                          bf16* __restrict__ k_pages, bf16* __restrict__ v_pages, int nq, int nkv, int hd, int rot_dim,
                          int page_size, int interleaved, int vd, const bf16* __restrict__ wq, const bf16* __restrict__ wk,
-                         int q_count, int k_count, float eps) {
+                         int q_count, int k_count, float eps, const float* __restrict__ bias, float* __restrict__ v_first,
+                         const float* __restrict__ lam, int mix_mode) {
     extern __shared__ float row[];            // [(nq + nkv) * hd] the token's q and k parts, [half] sines, [half] cosines
     __shared__ float scratch[32];
     pdl_launch_dependents();
@@ -456,7 +457,8 @@ rope_row_norm_vec_kernel(const bf16* __restrict__ qkv, int row_stride, bf16* __r
         float ss = 0.f;
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const float2 v = __bfloat1622float2(p2[e]);
+            float2 v = __bfloat1622float2(p2[e]);
+            if (bias) { v.x += bias[c0 + 2 * e]; v.y += bias[c0 + 2 * e + 1]; }      // the projection's bias joins the finished sum
             row[c0 + 2 * e] = v.x; row[c0 + 2 * e + 1] = v.y;
             ss += v.x * v.x; ss += v.y * v.y;
         }
@@ -500,10 +502,24 @@ rope_row_norm_vec_kernel(const bf16* __restrict__ qkv, int row_stride, bf16* __r
     }
     if (slot < 0) return;
     const int v_per = vd >> 3;
+    const float l = mix_mode == 2 ? lam[0] : 0.f;
     for (int item = threadIdx.x; item < nkv * v_per; item += blockDim.x) {
         const int kvh = item / v_per, c0 = (item % v_per) * 8;
-        *reinterpret_cast<uint4*>(v_pages + (((size_t)(slot / page_size) * nkv + kvh) * page_size + slot % page_size) * vd + c0) =
-            *reinterpret_cast<const uint4*>(x + qw + kw + kvh * vd + c0);
+        uint4 raw = *reinterpret_cast<const uint4*>(x + qw + kw + kvh * vd + c0);
+        if (bias != nullptr || mix_mode != 0) {
+            // as in the kernel above: the bias, then the values left for later layers (unrounded) or blended with an earlier layer's
+            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&raw);
+            float* keep = v_first + (size_t)t * nkv * vd + kvh * vd + c0;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float2 v = __bfloat1622float2(h2[e]);
+                if (bias) { v.x += bias[qw + kw + kvh * vd + c0 + 2 * e]; v.y += bias[qw + kw + kvh * vd + c0 + 2 * e + 1]; }
+                if (mix_mode == 1) { keep[2 * e] = v.x; keep[2 * e + 1] = v.y; }
+                else if (mix_mode == 2) { v.x = fmaf(l, keep[2 * e], (1.0f - l) * v.x); v.y = fmaf(l, keep[2 * e + 1], (1.0f - l) * v.y); }
+                h2[e] = __floats2bfloat162_rn(v.x, v.y);
+            }
+        }
+        *reinterpret_cast<uint4*>(v_pages + (((size_t)(slot / page_size) * nkv + kvh) * page_size + slot % page_size) * vd + c0) = raw;
     }
 }
 
@@ -537,7 +553,7 @@ WLLM_API int wllm_rope_row_norm_kv_write(const void* qkv, int in_dtype, int row_
             rot_dim, page_size, interleaved, vd, wq, wk, w_dtype, q_count, k_count, eps, bias, v_first, lam, mix_mode); \
     } while (0)
     const bool aligned = !(((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)wq | (uintptr_t)wk) & 15);
-    if (bias == nullptr && mix_mode == 0 && in_dtype == WLLM_BF16 && out_dtype == WLLM_BF16 && w_dtype == WLLM_BF16 && in_splits == 1 && aligned && hd % 8 == 0 &&
+    if (in_dtype == WLLM_BF16 && out_dtype == WLLM_BF16 && w_dtype == WLLM_BF16 && in_splits == 1 && aligned && hd % 8 == 0 &&
         vd % 8 == 0 && rot_dim % 8 == 0 && row_stride % 8 == 0 && q_stride % 8 == 0) {
         static bool raised = false;
         if (!raised && smem > 48 * 1024) {
@@ -547,7 +563,7 @@ WLLM_API int wllm_rope_row_norm_kv_write(const void* qkv, int in_dtype, int row_
         }
         return wllm_launch(rope_row_norm_vec_kernel, n, 256, smem, stream, (const bf16*)qkv, row_stride, (bf16*)q_out, q_stride,
                            positions, slots, inv_freq, (bf16*)k_pages, (bf16*)v_pages, nq, nkv, hd, rot_dim, page_size, interleaved,
-                           vd, (const bf16*)wq, (const bf16*)wk, q_count, k_count, eps);
+                           vd, (const bf16*)wq, (const bf16*)wk, q_count, k_count, eps, bias, v_first, lam, mix_mode);
     }
     if (in_dtype == WLLM_BF16 && out_dtype == WLLM_BF16) RN(bf16, bf16);
     if (in_dtype == WLLM_F32 && out_dtype == WLLM_BF16) RN(float, bf16);
