@@ -177,14 +177,14 @@ __device__ __forceinline__ void delta_token(float (&S)[NE], const float* __restr
 // next tile's rows are on their way while this one is walked; a key's and a query's rows are padded with zeros to 32 NE / 4
 // channels in shared memory, so the walk carries no guards.  k . q of a tile's tokens is worked out once a tile by the
 // warps together (it is the same for every column).
-template <int NE, int LPC>
-__global__ void __launch_bounds__(DR_THREADS)
+template <int NE, int LPC, int THREADS>
+__global__ void __launch_bounds__(THREADS)
 delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                   const float* __restrict__ beta, const float* __restrict__ decay, float* __restrict__ state,
                   float* __restrict__ out, const int* __restrict__ req_q_start, const int* __restrict__ req_q_len,
                   const int* __restrict__ req_slot, int H, int G, int D, int V) {
     constexpr int DP = LPC * NE;                        // channels of a row in shared memory
-    constexpr int DR_COLS = DR_THREADS / LPC;           // value columns of the CTA
+    constexpr int DR_COLS = THREADS / LPC;              // value columns of the CTA
     extern __shared__ __align__(16) float dr_smem[];    // two stages of [TT][DP] q, [TT][DP] k, [TT][16] v, [TT] beta, [TT] decay; [TT] k.q
     pdl_begin();
     const int r = blockIdx.z, h = blockIdx.y;
@@ -266,7 +266,7 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
         const float* bs = vs + DR_TT * DR_COLS;
         const float* gs = bs + DR_TT;
         const int count = min(DR_TT, len - tile * DR_TT);
-        for (int tt = warp; tt < count; tt += DR_THREADS / 32) {     // k . q: a lane's strided chain, the warp's tree
+        for (int tt = warp; tt < count; tt += THREADS / 32) {     // k . q: a lane's strided chain, the warp's tree
             float acc = 0.f;
             for (int c = lane; c < D; c += 32) acc = fmaf(ks[tt * DP + c], qs[tt * DP + c], acc);
             acc = warp_sum(acc);
@@ -339,20 +339,21 @@ WLLM_API int wllm_delta_scan(const float* q, const float* k, const float* v, con
     if (requests <= 0) return WLLM_OK;
     if (H <= 0 || H > 65535 || G <= 0 || H % G != 0 || requests > 65535 || D <= 0 || D > 256 || V <= 0) return WLLM_BAD_SIZE;
     // heads of up to 32 channels: eight lanes a column, four channels each; above: sixteen lanes, 4, 8 or 16 channels each
-    const int lpc = D <= 32 ? 8 : 16, ne = D <= 64 ? 4 : (D <= 128 ? 8 : 16), cols = DR_THREADS / lpc;
+    const int lpc = D <= 32 ? 8 : 16, ne = D <= 64 ? 4 : (D <= 128 ? 8 : 16), threads = DR_THREADS;
+    const int cols = threads / lpc;
     const dim3 grid((V + cols - 1) / cols, H, requests);
     const size_t smem = ((size_t)2 * DR_TT * (2 * lpc * ne + cols + 2) + DR_TT) * sizeof(float);
     static bool raised = false;
     if (!raised && smem > 48 * 1024) {
-        const cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<16, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        const cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<16, 16, DR_THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
         if (e != cudaSuccess) return 1000 + (int)e;
         raised = true;
     }
-#define SCAN(NE, LPC) wllm_launch(delta_scan_kernel<NE, LPC>, grid, DR_THREADS, smem, stream, q, k, v, beta, decay, state, out, \
-                                  req_q_start, req_q_len, req_slot, H, G, D, V)
-    if (D <= 32) return SCAN(4, 8);
-    if (D <= 64) return SCAN(4, 16);
-    if (D <= 128) return SCAN(8, 16);
-    return SCAN(16, 16);
+#define SCAN(NE, LPC, TH) wllm_launch(delta_scan_kernel<NE, LPC, TH>, grid, TH, smem, stream, q, k, v, beta, decay, state, out, \
+                                      req_q_start, req_q_len, req_slot, H, G, D, V)
+    if (D <= 32) return SCAN(4, 8, DR_THREADS);
+    if (D <= 64) return SCAN(4, 16, DR_THREADS);
+    if (D <= 128) return SCAN(8, 16, DR_THREADS);
+    return SCAN(16, 16, DR_THREADS);
 #undef SCAN
 }
