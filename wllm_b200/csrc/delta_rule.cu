@@ -3,9 +3,9 @@
 //
 //     S <- g_t S;    u_t = beta_t (v_t - S^T k_t);    S <- S + k_t u_t^T;    o_t = S^T q_t        S: [dim, vdim], 32-bit
 //
-// g_t in (0, 1) is one decay per head and token, beta_t in (0, 1) one step size per head and token.  q and k come through a
-// short causal convolution over time (per channel, `taps` taps, the last tap the token's own, zeros before the sequence's
-// start) and SiLU, and are made unit vectors per head; v comes through its convolution and SiLU.  Query and key heads may be
+// g_t in (0, 1) is one decay per head and token, beta_t in (0, 1) one step size per head and token.  q, k and v are each
+// filtered along the sequence, channel by channel, by `taps` taps that look back only (the last tap weighs the token itself,
+// inputs in front of the sequence count as zero) and pass SiLU; q and k are then scaled to unit length head by head.  Query and key heads may be
 // fewer than value heads (head h reads q/k head h / (H / G)).  The state and the convolutions' last taps - 1 inputs live in
 // the cache manager's state slots and are carried from step to step, so a whole prompt, a portion and a single decoded token
 // are one case and give the same bits.
@@ -18,7 +18,7 @@
 //                           hold a column (runs of four key channels each), a CTA of eight warps 32 or 16 columns of one
 //                           (request, head); tokens arrive in tiles through a cp.async ring and are walked in order.  With
 //                           a = S^T k and b = S^T q taken from the decayed state in one pass (two sums over a column's lanes),
-//                           u = beta (v - g a) and o = g b + u (k . q): the read-out sees the token's own write.
+//                           u = beta (v - g a) and o = g b + u (k . q), which is S^T q of the state that already holds the token's update.
 #include "common.cuh"
 
 __device__ __forceinline__ float dr_any(const void* p, int dtype, size_t i) {

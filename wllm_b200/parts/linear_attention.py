@@ -25,8 +25,8 @@ decays it, then corrects it towards its value along its key, then reads it with 
     S <- g_t S;    u_t = beta_t (v_t - S^T k_t);    S <- S + k_t u_t^T;    o_t = S^T q_t
 
 q, k (num_kv_heads heads of key_dim; value head h reads q/k head h // (num_heads / num_kv_heads)) and v (num_heads heads of
-value_dim) pass a short causal convolution over time per channel (`conv_taps` taps, the last one the token's own, zeros before
-the sequence's start; its last taps - 1 inputs are state too) and SiLU; q and k heads are divided by sqrt(sum(x^2) +
+value_dim) are each filtered along the sequence, channel by channel, by `conv_taps` taps that look back only (the last tap weighs
+the token itself, inputs in front of the sequence count as zero; the newest taps - 1 inputs are kept as state) and pass SiLU; q and k heads are divided by sqrt(sum(x^2) +
 unit_norm_eps), q is also multiplied by q_scale; beta_t = sigmoid(beta_proj x) and g_t = exp(-exp(decay_log) softplus(decay_proj x +
 decay_bias)), one of each per head.  Each head's o is divided by its root mean square over value_dim (eps), times the gain
 head_norm_weight shared by the heads, times silu(g_proj x); then o_proj.
