@@ -585,6 +585,28 @@ def test_experts_whose_inputs_carry_their_sigmoid_scores(sizes, dtype):
     assert n * top < part.TC_FROM_PAIRS or dtype == torch.float32 or ops.tc_grouped_ok(x.to(DEV), part.w_gu)
 
 
+def test_the_router_chooses_by_logits_where_sigmoid_scores_all_round_to_one():
+    """Logits of 20 to 60 all have a 32-bit sigmoid of exactly 1: the chosen experts are still those of the largest logits, in
+    their order, as in the 64-bit statement."""
+    from wllm_b200.kernels import ops
+    g = torch.Generator().manual_seed(9)
+    n, H, E, top = 40, 64, 8, 3
+    x = torch.randn(n, H, generator=g)
+    w = torch.randn(E, H, generator=g) * 0.2
+    w += 40.0 * x[0] / x[0].pow(2).sum()          # every expert's logit for token 0 is near 40
+    x[1:] = x[0] + 0.05 * torch.randn(n - 1, H, generator=g)
+    z = x.double() @ w.double().T
+    assert (torch.sigmoid(z.float()) == 1.0).all() and z.min() > 20
+    chosen = torch.empty(n, top, dtype=torch.int32, device=DEV)
+    weights = torch.empty(n, top, device=DEV)
+    ops.moe_route(x.to(DEV), w.to(DEV), None, chosen, weights, None, scores="sigmoid")
+    want = z.topk(top, dim=-1).indices
+    gaps = z.sort(-1, descending=True).values
+    clear = ((gaps[:, :top] - gaps[:, 1:top + 1]).abs() > 1e-3).all(-1)
+    assert clear.sum() > n // 2 and torch.equal(chosen.cpu().long()[clear], want[clear])
+    assert (weights.cpu() == 1.0).all()
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("sizes", [(64, 8, 3, 200), (50, 5, 2, 77), (128, 16, 4, 300)])
 def test_the_tokens_own_input(sizes, dtype):

@@ -17,7 +17,8 @@
 //            tokens' rows copied into sorted order (moe_gather) and the table of row tiles that the plan writes.
 //   combine  out[token] = sum over the token's ranks, in rank order, of weight * y[place] (+ gate * shared unit).
 //
-// Two more forms.  Scores: softmax over all experts, or (score_mode 1) sigmoid(z) expert by expert, not normalised.  Unit
+// Two more forms.  Scores: softmax over all experts, or (score_mode 1) sigmoid(z) expert by expert, not normalised (without
+// groups the experts are then chosen by z itself: the same order, and no ties where large logits all round to a score of 1).  Unit
 // (MODE 2): an expert without a gate, down(relu(up (s a))^2), whose input is multiplied by the pair's score s: the up product
 // is linear, so s multiplies its 32-bit sums in front of the activation; the combine then adds the experts' outputs as they are.
 //
@@ -84,6 +85,25 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w_router, co
         const int t = t0 + j;
         float* sc = sc_all + (size_t)j * E;
         float* gs = gs_all + (size_t)j * groups;
+        if (score_mode == 1 && groups == 1) {
+            // sigmoid scores without groups: the choice is made on the logits themselves (the sigmoid keeps their order, but
+            // large logits all round to a score of 1 and would tie); the weights are the chosen logits' sigmoids
+            for (int k = 0; k < top; ++k) {
+                float best = -INFINITY; int at = 0x7fffffff;
+                for (int e = lane; e < E; e += 32) { const float v = sc[e]; if (v > best || (v == best && e < at)) { best = v; at = e; } }
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float ob = __shfl_xor_sync(0xffffffffu, best, o); const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+                    if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+                }
+                if (lane == 0) {
+                    chosen[(size_t)t * top + k] = at;
+                    weights[(size_t)t * top + k] = 1.0f / (1.0f + expf(-best));
+                    sc[at] = -INFINITY;
+                }
+                __syncwarp();
+            }
+            continue;
+        }
         if (score_mode == 1) {
             for (int e = lane; e < E; e += 32) sc[e] = 1.0f / (1.0f + expf(-sc[e]));
         } else {

@@ -1142,7 +1142,8 @@ def delta_scan(q, k, v, beta, decay, state, out, req_q_start, req_q_len, req_slo
 def moe_route(x: torch.Tensor, w_router: torch.Tensor, w_gate, chosen: torch.Tensor, weights: torch.Tensor, gate_out,
               groups: int = 1, groups_kept: int = 1, scores: str = "softmax") -> None:
     """The router of routed experts (csrc/moe.cu): scores = softmax(w_router x) in 32-bit over all E experts (`scores`
-    'sigmoid': sigmoid(w_router x) expert by expert, not normalised), the choice
+    'sigmoid': sigmoid(w_router x) expert by expert, not normalised; without groups the choice is made on the logits, whose order
+    the sigmoid keeps, so that large logits that all round to a score of 1 do not tie), the choice
     limited to the `groups_kept` best of `groups` groups of neighbouring experts; chosen [n, top] (descending score) and
     weights [n, top] (the scores as they are).  With `w_gate` [H], gate_out[n] = sigmoid(w_gate . x)."""
     _need_cuda(x, w_router, w_gate, chosen, weights, gate_out)
